@@ -1,0 +1,14 @@
+"""dynamis_b200 — B200 (sm_100a) implementation of the Dynamis per-step data-parallel hot path.
+
+Radius graph, space-filling-curve partition, halo maps and halo exchange behind the reference's
+own Python-facing names.  The compute lives in ``libdynb.so`` (hand-written CUDA, C ABI in
+``include/dynb.h``); there is no CPU or PyTorch fallback.
+"""
+
+from .graph import (  # noqa: F401
+    radius_graph_pbc,
+    radius_graph_pbc_counts_ex,
+    radius_graph_pbc_cuda,
+    radius_graph_pbc_ex,
+    radius_graph_pbc_with_dist,
+)

@@ -1,0 +1,76 @@
+"""ctypes binding of libdynb.so (the C ABI declared in include/dynb.h).
+
+The library is the product: there is no fallback.  If it has not been built, importing
+``lib()`` raises with the build command.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+SO_PATH = os.path.join(_HERE, "libdynb.so")
+
+DYNB_F32 = 0
+DYNB_F64 = 1
+
+RG_SRC_OVERFLOW = 1
+RG_BAD_TARGET = 2
+RG_SHIFT_RANGE = 4
+RG_NONFINITE = 8
+
+_p = ctypes.c_void_p
+_i64 = ctypes.c_int64
+_i32 = ctypes.c_int
+_f64 = ctypes.c_double
+
+
+class RgHeader(ctypes.Structure):
+    _fields_ = [
+        ("E", ctypes.c_int64),
+        ("M", ctypes.c_int64),
+        ("status", ctypes.c_uint32),
+        ("max_degree", ctypes.c_uint32),
+        ("grid", ctypes.c_int32 * 3),
+        ("group_cells", ctypes.c_int32),
+        ("num_groups", ctypes.c_int64),
+        ("reserved", ctypes.c_int64 * 2),
+    ]
+
+
+# name -> (restype, argtypes); every symbol include/dynb.h declares must be listed here
+SIGNATURES = {
+    "dynb_last_error": (ctypes.c_char_p, []),
+    "dynb_version": (_i32, []),
+    "dynb_rg_suggest_capacity": (_i32, [_i64, _p, _p, _f64, _i32, ctypes.POINTER(_i64), ctypes.POINTER(_i64)]),
+    "dynb_rg_workspace_bytes": (_i32, [_i64, _i64, _i64, _i64, _i32, ctypes.POINTER(_i64)]),
+    "dynb_rg_plan": (_i32, [_p, _i32, _i64, _p, _p, _f64, _p, _i64, _p, _i64, _i64, _i64, _p, _p, _p]),
+    "dynb_rg_fill": (_i32, [_p, _i32, _p, _p, _p, _i64, _p]),
+}
+
+_LIB = None
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(SO_PATH):
+            raise RuntimeError(
+                f"{SO_PATH} is missing: build the CUDA library first with `python -m dynamis_b200.build` "
+                "(there is no CPU or PyTorch fallback)"
+            )
+        L = ctypes.CDLL(SO_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _LIB = L
+    return _LIB
+
+
+def check(rc: int, what: str = "") -> None:
+    if rc != 0:
+        msg = lib().dynb_last_error()
+        text = msg.decode() if msg else ""
+        raise RuntimeError(f"dynb {what} failed (code {rc}): {text}")

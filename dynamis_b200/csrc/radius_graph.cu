@@ -1,0 +1,886 @@
+// Periodic cell-list radius graph for B200 (sm_100a).
+//
+// Replaces the reference's radius_graph_pbc_cuda_impl_ex
+// (dynamis_state/src/csrc/graph/radius_graph_kernels.cu:479-934) behind the C ABI in dynb.h.
+//
+// Pipeline (one stream, no host synchronisation inside the plan):
+//   rg_wrap        wrap positions into the unit cell, classify which periodic images each atom
+//                  needs, reduce the bounding box of all images          (ref :596-605, :18-67)
+//   rg_grid        one thread: choose the cell grid on the device        (ref :662-692)
+//   rg_bin_count   histogram of images / targets per cell (atomics)      (ref :146-171)
+//   scan           cell starts
+//   rg_bin_scatter provisional slot inside each cell (atomic rank)
+//   rg_bin_finalize deterministic order inside each cell, write packed source / target records
+//   rg_pair<COUNT> per-target degree                                     (ref :197-258)
+//   scan           edge offsets + total
+//   rg_pair<FILL>  edges                                                 (ref :282-442)
+//
+// The edge SET is fixed by three predicates that are kept expression-for-expression identical to
+// the reference (same operand order, compiled with the same default FMA contraction): the wrap,
+// the periodic-image test with the image position, and d2 <= r2 && d2 > 1e-8f.  The cell grid
+// only decides which pairs are examined and is free to differ.
+//
+// Work decomposition of rg_pair: one warp owns a run of `group_cells` consecutive cells along x
+// and all targets inside.  It copies the (2*pad+1)^2 contiguous runs of neighbouring source
+// records into a dense shared-memory list once, then every target is tested against the dense
+// list with one candidate per lane (conflict-free 16-byte shared loads, ballot + popc
+// compaction).  Hits are parked in a small per-warp list and written out 32 edges at a time so
+// that the 8-byte index stores of a warp cover one contiguous 256-byte run.
+
+#include "common.cuh"
+#include "scan.cuh"
+
+#include <math.h>
+#include <string.h>
+
+namespace dynb {
+
+// ------------------------------------------------------------------------------------------
+// Device-resident plan header.  The first 64 bytes mirror dynb_rg_header.
+// ------------------------------------------------------------------------------------------
+struct DevHeader {
+    unsigned long long E;
+    unsigned long long M;
+    uint32_t status;
+    uint32_t max_degree;
+    int32_t nx, ny, nz;
+    int32_t group_cells;
+    unsigned long long num_groups;
+    long long reserved[2];
+    // ---- internal -----------------------------------------------------------------------
+    uint32_t ncell_plus1;
+    int32_t pad;
+    int32_t gx;
+    int32_t unused;
+    unsigned long long bb_min[3];  // ordered-integer images of the bounding box
+    unsigned long long bb_max[3];
+    double gmin[3];
+    double res_inv;
+};
+static_assert(offsetof(DevHeader, ncell_plus1) == sizeof(dynb_rg_header), "public header prefix mismatch");
+
+constexpr uint32_t RG_FATAL = DYNB_RG_SRC_OVERFLOW | DYNB_RG_BAD_TARGET | DYNB_RG_NONFINITE | DYNB_RG_SHIFT_RANGE;
+
+template <typename T> struct Geom {
+    T inv[9];
+    T cell[9];
+    T cf[3];
+    int rep[3];
+    int pbc[3];
+};
+
+// Rounded-once helpers (no contraction across them).
+__device__ __forceinline__ float mul_rn(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ double mul_rn(double a, double b) { return __dmul_rn(a, b); }
+__device__ __forceinline__ float fma_rn(float a, float b, float c) { return __fmaf_rn(a, b, c); }
+__device__ __forceinline__ double fma_rn(double a, double b, double c) { return __fma_rn(a, b, c); }
+__device__ __forceinline__ float sub_rn(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ double sub_rn(double a, double b) { return __dsub_rn(a, b); }
+__device__ __forceinline__ float floor_t(float a) { return floorf(a); }
+__device__ __forceinline__ double floor_t(double a) { return floor(a); }
+__device__ __forceinline__ bool finite_t(float a) { return isfinite(a); }
+__device__ __forceinline__ bool finite_t(double a) { return isfinite(a); }
+
+__device__ __forceinline__ unsigned long long ordered_any(float v) { return (unsigned long long)ordered_u32(v); }
+__device__ __forceinline__ unsigned long long ordered_any(double v) { return ordered_u64(v); }
+template <typename T> __device__ __forceinline__ double unordered_any(unsigned long long u);
+template <> __device__ __forceinline__ double unordered_any<float>(unsigned long long u) { return (double)unordered_f32((uint32_t)u); }
+template <> __device__ __forceinline__ double unordered_any<double>(unsigned long long u) { return unordered_f64(u); }
+
+// K = 3 inner product exactly as an fp32/fp64 GEMM accumulates it: k-sequential FMA chain.
+// The reference wraps positions with two at::mm calls (radius_graph_kernels.cu:602,605).
+template <typename T> __device__ __forceinline__ T dot3_gemm(T a0, T b0, T a1, T b1, T a2, T b2)
+{
+    return fma_rn(a2, b2, fma_rn(a1, b1, mul_rn(a0, b0)));
+}
+
+// Image position, same expression shape as the reference's write_pbc_images_kernel (:122-128).
+template <typename T>
+__device__ __forceinline__ void image_pos(const Geom<T>& g, T px, T py, T pz, int dx, int dy, int dz, T& x, T& y, T& z)
+{
+    T shift_x = (T)dx * g.cell[0] + (T)dy * g.cell[3] + (T)dz * g.cell[6];
+    T shift_y = (T)dx * g.cell[1] + (T)dy * g.cell[4] + (T)dz * g.cell[7];
+    T shift_z = (T)dx * g.cell[2] + (T)dy * g.cell[5] + (T)dz * g.cell[8];
+    x = px + shift_x;
+    y = py + shift_y;
+    z = pz + shift_z;
+}
+
+// flags: bit d = "may be shifted up along d", bit 3+d = "may be shifted down along d"
+__device__ __forceinline__ bool image_needed(uint32_t flags, int dx, int dy, int dz)
+{
+    bool ok = true;
+    if (dx > 0) ok = ok && (flags & 1u); else if (dx < 0) ok = ok && (flags & 8u);
+    if (dy > 0) ok = ok && (flags & 2u); else if (dy < 0) ok = ok && (flags & 16u);
+    if (dz > 0) ok = ok && (flags & 4u); else if (dz < 0) ok = ok && (flags & 32u);
+    return ok;
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t cell_of(const DevHeader& h, T x, T y, T z)
+{
+    const T ri = (T)h.res_inv;
+    int cx = (int)floor_t((x - (T)h.gmin[0]) * ri);
+    int cy = (int)floor_t((y - (T)h.gmin[1]) * ri);
+    int cz = (int)floor_t((z - (T)h.gmin[2]) * ri);
+    cx = max(0, min(cx, h.nx - 1));
+    cy = max(0, min(cy, h.ny - 1));
+    cz = max(0, min(cz, h.nz - 1));
+    return (uint32_t)cx + (uint32_t)h.nx * ((uint32_t)cy + (uint32_t)h.ny * (uint32_t)cz);
+}
+
+// ------------------------------------------------------------------------------------------
+// rg_wrap
+// ------------------------------------------------------------------------------------------
+constexpr int WRAP_THREADS = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(WRAP_THREADS)
+rg_wrap_kernel(const T* __restrict__ pos, int64_t N, Geom<T> g, int vec_ok, Vec4<T>* __restrict__ posw,
+               int4* __restrict__ aff, DevHeader* __restrict__ h)
+{
+    __shared__ T stage[WRAP_THREADS * 3];
+    __shared__ unsigned long long red[6][WRAP_THREADS / 32];
+    __shared__ unsigned int red_cnt[WRAP_THREADS / 32];
+
+    const int64_t block_base = (int64_t)blockIdx.x * WRAP_THREADS;
+    const int64_t i = block_base + threadIdx.x;
+    const int64_t nblock = min((int64_t)WRAP_THREADS, N - block_base);
+
+    // Coalesced 16-byte loads of this block's 3*nblock reals, then a conflict-free stride-3 read.
+    {
+        const T* src = pos + block_base * 3;
+        const int nreal = (int)nblock * 3;
+        constexpr int PER = 16 / (int)sizeof(T);
+        if (vec_ok && nblock == WRAP_THREADS) {
+            using V = typename std::conditional<sizeof(T) == 4, float4, double2>::type;
+            const V* src4 = reinterpret_cast<const V*>(src);
+            V* dst4 = reinterpret_cast<V*>(stage);
+            for (int k = threadIdx.x; k < nreal / PER; k += WRAP_THREADS) dst4[k] = src4[k];
+        } else {
+            for (int k = threadIdx.x; k < nreal; k += WRAP_THREADS) stage[k] = src[k];
+        }
+    }
+    __syncthreads();
+
+    unsigned long long mn[3] = {~0ull, ~0ull, ~0ull}, mx[3] = {0ull, 0ull, 0ull};
+    unsigned int count = 0;
+    uint32_t status = 0;
+
+    if (i < N) {
+        const T px = stage[threadIdx.x * 3 + 0], py = stage[threadIdx.x * 3 + 1], pz = stage[threadIdx.x * 3 + 2];
+        T f[3], m[3];
+#pragma unroll
+        for (int k = 0; k < 3; k++) f[k] = floor_t(dot3_gemm(px, g.inv[k], py, g.inv[3 + k], pz, g.inv[6 + k]));
+#pragma unroll
+        for (int k = 0; k < 3; k++) m[k] = dot3_gemm(f[0], g.cell[k], f[1], g.cell[3 + k], f[2], g.cell[6 + k]);
+        const T wx = sub_rn(px, m[0]), wy = sub_rn(py, m[1]), wz = sub_rn(pz, m[2]);
+
+        if (!(finite_t(wx) && finite_t(wy) && finite_t(wz))) status |= DYNB_RG_NONFINITE;
+        const T lim = (T)1048576.0;
+        if (!(fabs(f[0]) < lim && fabs(f[1]) < lim && fabs(f[2]) < lim)) status |= DYNB_RG_SHIFT_RANGE;
+
+        // Fractional coordinates of the wrapped position, reference expression (:36-38).
+        T s[3];
+        s[0] = wx * g.inv[0] + wy * g.inv[3] + wz * g.inv[6];
+        s[1] = wx * g.inv[1] + wy * g.inv[4] + wz * g.inv[7];
+        s[2] = wx * g.inv[2] + wy * g.inv[5] + wz * g.inv[8];
+        uint32_t flags = 0;
+#pragma unroll
+        for (int d = 0; d < 3; d++) {
+            if (g.pbc[d]) {
+                if (!(s[d] >= g.cf[d])) flags |= (1u << d);                 // :55
+                if (!(s[d] <= (T)1.0f - g.cf[d])) flags |= (8u << d);       // :58
+            }
+        }
+        if (!(status & DYNB_RG_NONFINITE)) {
+            for (int dx = -g.rep[0]; dx <= g.rep[0]; dx++)
+                for (int dy = -g.rep[1]; dy <= g.rep[1]; dy++)
+                    for (int dz = -g.rep[2]; dz <= g.rep[2]; dz++) {
+                        if (!image_needed(flags, dx, dy, dz)) continue;
+                        T x, y, z;
+                        image_pos(g, wx, wy, wz, dx, dy, dz, x, y, z);
+                        unsigned long long ox = ordered_any(x), oy = ordered_any(y), oz = ordered_any(z);
+                        mn[0] = min(mn[0], ox); mx[0] = max(mx[0], ox);
+                        mn[1] = min(mn[1], oy); mx[1] = max(mx[1], oy);
+                        mn[2] = min(mn[2], oz); mx[2] = max(mx[2], oz);
+                        count++;
+                    }
+        }
+        Vec4<T> w;
+        w.x = wx; w.y = wy; w.z = wz; w.w = bits_to_real((int32_t)flags, T());
+        posw[i] = w;
+        aff[i] = make_int4((int)f[0], (int)f[1], (int)f[2], (int)count);
+    }
+
+    // block reduction
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            mn[k] = min(mn[k], __shfl_xor_sync(0xffffffffu, mn[k], o));
+            mx[k] = max(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], o));
+        }
+        count += __shfl_xor_sync(0xffffffffu, count, o);
+        status |= __shfl_xor_sync(0xffffffffu, status, o);
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < 3; k++) { red[k][warp] = mn[k]; red[3 + k][warp] = mx[k]; }
+        red_cnt[warp] = count;
+        if (status) atomicOr(&h->status, status);
+    }
+    __syncthreads();
+    if (threadIdx.x < 6) {
+        unsigned long long v = red[threadIdx.x][0];
+        for (int w = 1; w < WRAP_THREADS / 32; w++)
+            v = (threadIdx.x < 3) ? min(v, red[threadIdx.x][w]) : max(v, red[threadIdx.x][w]);
+        if (threadIdx.x < 3) atomicMin(&h->bb_min[threadIdx.x], v);
+        else atomicMax(&h->bb_max[threadIdx.x - 3], v);
+    } else if (threadIdx.x == 6) {
+        unsigned long long c = 0;
+        for (int w = 0; w < WRAP_THREADS / 32; w++) c += red_cnt[w];
+        if (c) atomicAdd(&h->M, c);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// rg_grid: one thread chooses the grid.  Cells of edge radius/1.99 scanned +-2 (as the
+// reference, :662,776) unless that would need more than cell_capacity cells; then the cells
+// grow, and once they are wider than the cutoff the scan shrinks to +-1.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rg_grid_kernel(DevHeader* h, double radius, long long src_capacity, long long cell_capacity)
+{
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    if (h->M > (unsigned long long)src_capacity) h->status |= DYNB_RG_SRC_OVERFLOW;
+    if (h->M == 0 || (h->status & RG_FATAL)) {
+        h->nx = h->ny = h->nz = 1;
+        h->ncell_plus1 = 2;
+        h->pad = 1;
+        h->group_cells = 1;
+        h->gx = 1;
+        h->num_groups = 0;
+        h->gmin[0] = h->gmin[1] = h->gmin[2] = 0.0;
+        h->res_inv = 1.0;
+        return;
+    }
+    double lo[3], ext[3];
+    for (int k = 0; k < 3; k++) {
+        lo[k] = unordered_any<T>(h->bb_min[k]) - 0.01;
+        ext[k] = unordered_any<T>(h->bb_max[k]) + 0.01 - lo[k];
+    }
+    double res = radius / 1.99;
+    long long n[3];
+    for (int it = 0; it < 400; it++) {
+        double tot = 1.0;
+        for (int k = 0; k < 3; k++) {
+            double c = ceil(ext[k] / res);
+            if (!(c >= 1.0)) c = 1.0;
+            if (c > 2.0e9) c = 2.0e9;
+            n[k] = (long long)c;
+            tot *= c;
+        }
+        if (tot + 1.0 <= (double)cell_capacity) break;
+        res *= 1.2;
+        if (it == 399) { n[0] = n[1] = n[2] = 1; }
+    }
+    h->nx = (int)n[0]; h->ny = (int)n[1]; h->nz = (int)n[2];
+    const long long ncell = n[0] * n[1] * n[2];
+    h->ncell_plus1 = (uint32_t)(ncell + 1);
+    const int pad = (res >= radius * 1.001) ? 1 : 2;
+    h->pad = pad;
+    for (int k = 0; k < 3; k++) h->gmin[k] = lo[k];
+    h->res_inv = 1.0 / res;
+    // cells per warp work item: keep the expected dense candidate list near 300 records
+    const double avg = (double)h->M / (double)ncell;
+    const double rows = (double)((2 * pad + 1) * (2 * pad + 1));
+    int S = (int)floor(300.0 / (rows * (avg > 1e-6 ? avg : 1e-6))) - 2 * pad;
+    S = S < 1 ? 1 : (S > 4 ? 4 : S);
+    if (S > h->nx) S = h->nx;
+    h->group_cells = S;
+    h->gx = (h->nx + S - 1) / S;
+    h->num_groups = (unsigned long long)h->gx * (unsigned long long)h->ny * (unsigned long long)h->nz;
+}
+
+// ------------------------------------------------------------------------------------------
+// binning
+// ------------------------------------------------------------------------------------------
+template <typename T, bool SCATTER>
+__global__ void __launch_bounds__(256)
+rg_bin_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ targets, Geom<T> g,
+              const Vec4<T>* __restrict__ posw, DevHeader* __restrict__ hp,
+              uint32_t* __restrict__ ccount, uint32_t* __restrict__ cfill,
+              uint32_t* __restrict__ tccount, uint32_t* __restrict__ tcfill,
+              unsigned long long* __restrict__ skey, uint32_t* __restrict__ scell,
+              uint32_t* __restrict__ tkey, uint32_t* __restrict__ tcell)
+{
+    const DevHeader h = *hp;
+    if (h.status & RG_FATAL) return;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < N) {
+        const Vec4<T> w = posw[i];
+        const uint32_t flags = (uint32_t)real_to_bits(w.w);
+        const int k1 = 2 * g.rep[1] + 1, k2 = 2 * g.rep[2] + 1;
+        const unsigned long long K = (unsigned long long)(2 * g.rep[0] + 1) * k1 * k2;
+        for (int dx = -g.rep[0]; dx <= g.rep[0]; dx++)
+            for (int dy = -g.rep[1]; dy <= g.rep[1]; dy++)
+                for (int dz = -g.rep[2]; dz <= g.rep[2]; dz++) {
+                    if (!image_needed(flags, dx, dy, dz)) continue;
+                    T x, y, z;
+                    image_pos(g, w.x, w.y, w.z, dx, dy, dz, x, y, z);
+                    const uint32_t c = cell_of(h, x, y, z);
+                    if (!SCATTER) {
+                        atomicAdd(&ccount[c], 1u);
+                    } else {
+                        const uint32_t slot = ccount[c] + atomicAdd(&cfill[c], 1u);
+                        const unsigned code = (unsigned)(((dx + g.rep[0]) * k1 + (dy + g.rep[1])) * k2 + (dz + g.rep[2]));
+                        skey[slot] = (unsigned long long)i * K + code;
+                        scell[slot] = c;
+                    }
+                }
+    }
+    if (i < Nt) {
+        const int64_t a = targets ? targets[i] : i;
+        if (a < 0 || a >= N) {
+            atomicOr(&hp->status, DYNB_RG_BAD_TARGET);
+        } else {
+            const Vec4<T> w = posw[a];
+            const uint32_t c = cell_of(h, w.x, w.y, w.z);
+            if (!SCATTER) {
+                atomicAdd(&tccount[c], 1u);
+            } else {
+                const uint32_t slot = tccount[c] + atomicAdd(&tcfill[c], 1u);
+                tkey[slot] = (uint32_t)i;
+                tcell[slot] = c;
+            }
+        }
+    }
+}
+
+// Deterministic order inside each cell (ascending key) and the packed records.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rg_bin_finalize_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ targets, Geom<T> g,
+                       const Vec4<T>* __restrict__ posw, const int4* __restrict__ aff,
+                       DevHeader* __restrict__ hp, const uint32_t* __restrict__ cstart,
+                       const uint32_t* __restrict__ tcstart, const unsigned long long* __restrict__ skey,
+                       const uint32_t* __restrict__ scell, const uint32_t* __restrict__ tkey,
+                       const uint32_t* __restrict__ tcell, Vec4<T>* __restrict__ spos,
+                       short4* __restrict__ scode, Vec4<T>* __restrict__ tpos, int4* __restrict__ tmeta)
+{
+    const DevHeader h = *hp;
+    if (h.status & RG_FATAL) return;
+    const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < (int64_t)h.M) {
+        const uint32_t c = scell[j];
+        const unsigned long long key = skey[j];
+        const uint32_t b = cstart[c], e = cstart[c + 1];
+        uint32_t rank = 0;
+        for (uint32_t q = b; q < e; q++) rank += (skey[q] < key) ? 1u : 0u;
+        const int k1 = 2 * g.rep[1] + 1, k2 = 2 * g.rep[2] + 1;
+        const unsigned long long K = (unsigned long long)(2 * g.rep[0] + 1) * k1 * k2;
+        const int64_t atom = (int64_t)(key / K);
+        unsigned code = (unsigned)(key % K);
+        const int dz = (int)(code % k2) - g.rep[2]; code /= k2;
+        const int dy = (int)(code % k1) - g.rep[1]; code /= k1;
+        const int dx = (int)code - g.rep[0];
+        const Vec4<T> w = posw[atom];
+        const int4 ff = aff[atom];
+        Vec4<T> r;
+        image_pos(g, w.x, w.y, w.z, dx, dy, dz, r.x, r.y, r.z);
+        r.w = bits_to_real((int32_t)atom, T());
+        spos[b + rank] = r;
+        const int ex = dx - ff.x, ey = dy - ff.y, ez = dz - ff.z;
+        if (ex < -32767 || ex > 32767 || ey < -32767 || ey > 32767 || ez < -32767 || ez > 32767)
+            atomicOr(&hp->status, DYNB_RG_SHIFT_RANGE);
+        scode[b + rank] = make_short4((short)ex, (short)ey, (short)ez, 0);
+    }
+    if (j < Nt) {
+        const uint32_t c = tcell[j];
+        const uint32_t ent = tkey[j];
+        const uint32_t b = tcstart[c], e = tcstart[c + 1];
+        uint32_t rank = 0;
+        for (uint32_t q = b; q < e; q++) rank += (tkey[q] < ent) ? 1u : 0u;
+        const int64_t a = targets ? targets[ent] : (int64_t)ent;
+        const Vec4<T> w = posw[a];
+        const int4 ff = aff[a];
+        Vec4<T> r;
+        r.x = w.x; r.y = w.y; r.z = w.z; r.w = bits_to_real((int32_t)ent, T());
+        tpos[b + rank] = r;
+        tmeta[b + rank] = make_int4((int)a, ff.x, ff.y, ff.z);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// rg_pair: the cell scan.
+// ------------------------------------------------------------------------------------------
+constexpr int PAIR_WARPS = 8;
+constexpr int PAIR_THREADS = PAIR_WARPS * 32;
+constexpr int PAIR_CAND_BYTES = 6144;  // dense candidate list per warp
+constexpr int PAIR_LIST = 128;         // parked hits per warp
+constexpr int PAIR_WARP_BYTES = PAIR_CAND_BYTES + PAIR_LIST * 2;
+
+enum { MODE_COUNT = 0, MODE_FILL = 1 };
+
+template <typename T> struct PairParams {
+    const DevHeader* h;
+    const uint32_t* cstart;
+    const uint32_t* tcstart;
+    const Vec4<T>* spos;
+    const short4* scode;
+    const Vec4<T>* tpos;
+    const int4* tmeta;
+    uint32_t* tcount;         // [Nt+1] degree per sorted target; running cursor in FILL
+    const long long* toffset; // [Nt+1]
+    T r2;
+};
+// The plan stores its PairParams inside the workspace (after the header) so that the fill call
+// needs nothing but the workspace pointer.
+constexpr int64_t RG_PARAMS_OFFSET = 512;
+constexpr int64_t RG_HEADER_BYTES = 1024;
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(PAIR_THREADS)
+rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restrict__ ei, float* __restrict__ shifts,
+               T* __restrict__ d2out, const long long E)
+{
+    const PairParams<T> p = *params_dev;
+    extern __shared__ __align__(32) unsigned char smem_raw[];
+    constexpr int CAP = PAIR_CAND_BYTES / (int)sizeof(Vec4<T>);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    Vec4<T>* cand = reinterpret_cast<Vec4<T>*>(smem_raw + warp * PAIR_WARP_BYTES);
+    unsigned short* list = reinterpret_cast<unsigned short*>(smem_raw + warp * PAIR_WARP_BYTES + PAIR_CAND_BYTES);
+
+    const DevHeader h = *p.h;
+    if (h.status & RG_FATAL) return;
+    const int nx = h.nx, ny = h.ny, nz = h.nz, S = h.group_cells, gx = h.gx, pad = h.pad;
+    const int Wd = 2 * pad + 1, nrun = Wd * Wd;
+    const T r2 = p.r2;
+    const T eps = (T)1e-8f;
+    const uint32_t lt = lanemask_lt();
+
+    const unsigned long long nwarps = (unsigned long long)gridDim.x * PAIR_WARPS;
+    for (unsigned long long grp = (unsigned long long)blockIdx.x * PAIR_WARPS + warp; grp < h.num_groups; grp += nwarps) {
+        const int ix = (int)(grp % (unsigned long long)gx);
+        const unsigned long long row = grp / (unsigned long long)gx;
+        const int cy = (int)(row % (unsigned long long)ny), cz = (int)(row / (unsigned long long)ny);
+        const int cx0 = ix * S, cx1 = min(cx0 + S, nx) - 1;
+        const uint32_t cbase = ((uint32_t)cz * ny + cy) * nx;
+        const uint32_t t0 = p.tcstart[cbase + cx0], t1 = p.tcstart[cbase + cx1 + 1];
+        if (t0 == t1) continue;
+
+        // contiguous source runs: lane r owns run (dy, dz)
+        int run_a = 0, run_len = 0;
+        if (lane < nrun) {
+            const int yy = cy + (lane % Wd) - pad, zz = cz + (lane / Wd) - pad;
+            if (yy >= 0 && yy < ny && zz >= 0 && zz < nz) {
+                const uint32_t b = ((uint32_t)zz * ny + yy) * nx;
+                const uint32_t a = p.cstart[b + max(cx0 - pad, 0)];
+                const uint32_t e = p.cstart[b + min(cx1 + pad, nx - 1) + 1];
+                run_a = (int)a;
+                run_len = (int)(e - a);
+            }
+        }
+        int L;
+        const int run_off = warp_excl_scan(run_len, lane, &L);
+
+        for (int cbeg = 0, chunk = 0; cbeg < L; cbeg += CAP, chunk++) {
+            const int clen = min(CAP, L - cbeg);
+            const int clen32 = (clen + 31) & ~31;
+            __syncwarp();
+            // dense staging: slot j holds the record of flattened candidate cbeg + j
+            for (int j = lane; j < clen32; j += 32) {
+                const int jj = cbeg + j;
+                int r = 0;
+#pragma unroll
+                for (int step = 16; step >= 1; step >>= 1) {
+                    const int cr = r + step;
+                    const int o = __shfl_sync(0xffffffffu, run_off, cr & 31);
+                    if (cr < 32 && o <= jj) r = cr;
+                }
+                const int ra = __shfl_sync(0xffffffffu, run_a, r);
+                const int ro = __shfl_sync(0xffffffffu, run_off, r);
+                Vec4<T> c;
+                if (j < clen) {
+                    const int gidx = ra + (jj - ro);
+                    c = p.spos[gidx];
+                    c.w = bits_to_real((int32_t)gidx, T());
+                } else {
+                    c.x = c.y = c.z = (T)3.0e38f;  // never within the cutoff
+                    c.w = (T)0;
+                }
+                cand[j] = c;
+            }
+            __syncwarp();
+
+            for (uint32_t t = t0; t < t1; t++) {
+                const Vec4<T> tp = p.tpos[t];
+                const T tx = tp.x, ty = tp.y, tz = tp.z;
+                int produced = (chunk == 0) ? 0 : (int)p.tcount[t];
+                int cnt = 0;
+                int4 tm;
+                long long base = 0;
+                if (MODE == MODE_FILL) {
+                    tm = p.tmeta[t];
+                    base = p.toffset[t];
+                }
+                for (int k = 0; k < clen32; k += 32) {
+                    const int j = k + lane;
+                    const Vec4<T> c = cand[j];
+                    const T sx = c.x, sy = c.y, sz = c.z;
+                    const T d2 = (tx - sx) * (tx - sx) + (ty - sy) * (ty - sy) + (tz - sz) * (tz - sz);
+                    const bool hit = (d2 <= r2) && (d2 > eps);
+                    const uint32_t mask = __ballot_sync(0xffffffffu, hit);
+                    if (MODE == MODE_FILL) {
+                        if (hit) list[cnt + __popc(mask & lt)] = (unsigned short)j;
+                    }
+                    cnt += __popc(mask);
+                    if (MODE == MODE_FILL) {
+                        if (cnt > PAIR_LIST - 32 || k + 32 >= clen32) {
+                            __syncwarp();
+                            for (int i = lane; i < cnt; i += 32) {
+                                const int jh = list[i];
+                                const Vec4<T> ch = cand[jh];
+                                const int gidx = real_to_bits(ch.w);
+                                const int atom = real_to_bits(p.spos[gidx].w);
+                                const short4 code = p.scode[gidx];
+                                const long long e = base + produced + i;
+                                ei[e] = (long long)atom;
+                                ei[E + e] = (long long)tm.x;
+                                shifts[3 * e + 0] = (float)((int)code.x + tm.y);
+                                shifts[3 * e + 1] = (float)((int)code.y + tm.z);
+                                shifts[3 * e + 2] = (float)((int)code.z + tm.w);
+                                if (d2out != nullptr) {
+                                    const T hx = ch.x, hy = ch.y, hz = ch.z;
+                                    d2out[e] = (tx - hx) * (tx - hx) + (ty - hy) * (ty - hy) + (tz - hz) * (tz - hz);
+                                }
+                            }
+                            produced += cnt;
+                            cnt = 0;
+                            __syncwarp();
+                        }
+                    }
+                }
+                if (MODE == MODE_COUNT) {
+                    if (lane == 0) p.tcount[t] = (uint32_t)(produced + cnt);
+                } else {
+                    if (lane == 0 && cbeg + CAP < L) p.tcount[t] = (uint32_t)produced;
+                }
+            }
+        }
+        // a group whose neighbourhood holds no source at all still owes its targets a zero
+        if (MODE == MODE_COUNT && L == 0) {
+            for (uint32_t t = t0 + lane; t < t1; t += 32) p.tcount[t] = 0;
+        }
+    }
+}
+
+// degree in caller order + maximum degree
+template <typename T>
+__global__ void __launch_bounds__(256)
+rg_post_count_kernel(int64_t Nt, const Vec4<T>* __restrict__ tpos, const uint32_t* __restrict__ tcount,
+                     int32_t* __restrict__ counts_out, DevHeader* __restrict__ h)
+{
+    if (h->status & RG_FATAL) return;
+    const int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    uint32_t c = 0;
+    if (k < Nt) {
+        c = tcount[k];
+        if (counts_out != nullptr) counts_out[real_to_bits(tpos[k].w)] = (int32_t)c;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c = max(c, __shfl_xor_sync(0xffffffffu, c, o));
+    if ((threadIdx.x & 31) == 0 && c > 0) atomicMax(&h->max_degree, c);
+}
+
+__global__ void rg_zero_counts_kernel(int64_t Nt, int32_t* counts_out)
+{
+    const int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (k < Nt) counts_out[k] = 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+struct RgLayout {
+    int64_t hdr, posw, aff, ccount, cfill, tccount, tcfill, skey, scell, spos, scode, tkey, tcell, tpos, tmeta,
+        tcount, toffset, sums, total;
+};
+
+static RgLayout rg_layout(int64_t N, int64_t Nt, int64_t src_cap, int64_t cell_cap, int dtype)
+{
+    const int64_t v4 = dtype == DYNB_F64 ? 32 : 16;
+    RgLayout L;
+    int64_t o = 0;
+    auto take = [&](int64_t bytes) { int64_t r = o; o = align_up(o + bytes, 256); return r; };
+    L.hdr = take(RG_HEADER_BYTES);
+    // zero-initialised block: cell counters (contiguous so that one memset clears them)
+    L.ccount = take((cell_cap + 2) * 4);
+    L.cfill = take((cell_cap + 2) * 4);
+    L.tccount = take((cell_cap + 2) * 4);
+    L.tcfill = take((cell_cap + 2) * 4);
+    L.posw = take(N * v4);
+    L.aff = take(N * 16);
+    L.skey = take(src_cap * 8);
+    L.scell = take(src_cap * 4);
+    L.spos = take(src_cap * v4);
+    L.scode = take(src_cap * 8);
+    L.tkey = take(Nt * 4);
+    L.tcell = take(Nt * 4);
+    L.tpos = take(Nt * v4);
+    L.tmeta = take(Nt * 16);
+    L.tcount = take((Nt + 1) * 4);
+    L.toffset = take((Nt + 2) * 8);
+    const int64_t tiles = std::max<int64_t>(scan_num_tiles(cell_cap + 2), scan_num_tiles(Nt + 2)) + 1;
+    L.sums = take(tiles * 8 * 2);
+    L.total = o;
+    return L;
+}
+
+// Host cell geometry in the precision of the positions, following the reference's host code
+// (radius_graph_kernels.cu:516-587): face distances, replication counts, cutoff fractions and
+// the cofactor inverse.  This translation unit is compiled with -ffp-contract=off for the host.
+template <typename T>
+static void rg_geometry(const T* cell, const uint8_t* pbc, T radius, Geom<T>& g)
+{
+    const T* a0 = cell; const T* a1 = cell + 3; const T* a2 = cell + 6;
+    T c12[3] = {a1[1] * a2[2] - a1[2] * a2[1], a1[2] * a2[0] - a1[0] * a2[2], a1[0] * a2[1] - a1[1] * a2[0]};
+    T vol = a0[0] * c12[0] + a0[1] * c12[1] + a0[2] * c12[2];
+    T abs_vol = std::abs(vol);
+    T c20[3] = {a2[1] * a0[2] - a2[2] * a0[1], a2[2] * a0[0] - a2[0] * a0[2], a2[0] * a0[1] - a2[1] * a0[0]};
+    T c01[3] = {a0[1] * a1[2] - a0[2] * a1[1], a0[2] * a1[0] - a0[0] * a1[2], a0[0] * a1[1] - a0[1] * a1[0]};
+    T n12 = std::sqrt(c12[0] * c12[0] + c12[1] * c12[1] + c12[2] * c12[2]);
+    T n20 = std::sqrt(c20[0] * c20[0] + c20[1] * c20[1] + c20[2] * c20[2]);
+    T n01 = std::sqrt(c01[0] * c01[0] + c01[1] * c01[1] + c01[2] * c01[2]);
+    T d_face[3] = {abs_vol / n12, abs_vol / n20, abs_vol / n01};
+    for (int d = 0; d < 3; d++) {
+        g.pbc[d] = pbc[d] ? 1 : 0;
+        if (pbc[d]) {
+            g.rep[d] = (int)std::ceil(radius / d_face[d]);
+            g.cf[d] = radius / d_face[d];
+        } else {
+            g.rep[d] = 0;
+            g.cf[d] = (T)0;
+        }
+    }
+    T inv_vol = (T)1 / vol;
+    g.inv[0] = (a1[1] * a2[2] - a1[2] * a2[1]) * inv_vol;
+    g.inv[1] = (a0[2] * a2[1] - a0[1] * a2[2]) * inv_vol;
+    g.inv[2] = (a0[1] * a1[2] - a0[2] * a1[1]) * inv_vol;
+    g.inv[3] = (a1[2] * a2[0] - a1[0] * a2[2]) * inv_vol;
+    g.inv[4] = (a0[0] * a2[2] - a0[2] * a2[0]) * inv_vol;
+    g.inv[5] = (a0[2] * a1[0] - a0[0] * a1[2]) * inv_vol;
+    g.inv[6] = (a1[0] * a2[1] - a1[1] * a2[0]) * inv_vol;
+    g.inv[7] = (a0[1] * a2[0] - a0[0] * a2[1]) * inv_vol;
+    g.inv[8] = (a0[0] * a1[1] - a0[1] * a1[0]) * inv_vol;
+    for (int i = 0; i < 9; i++) g.cell[i] = cell[i];
+}
+
+template <typename T>
+static int rg_geometry_checked(const void* cell_host, const uint8_t* pbc_host, double radius, Geom<T>& g)
+{
+    if (cell_host == nullptr || pbc_host == nullptr) return fail_arg("cell and pbc must not be null");
+    if (!(radius > 0.0)) return fail_arg("radius must be positive");
+    rg_geometry<T>(static_cast<const T*>(cell_host), pbc_host, (T)radius, g);
+    for (int d = 0; d < 3; d++) {
+        if (!(g.rep[d] >= 0 && g.rep[d] <= 64) || !std::isfinite((double)g.cf[d]))
+            return fail_arg("degenerate cell: a periodic axis needs more than 64 image layers (or the cell is singular)");
+    }
+    for (int i = 0; i < 9; i++)
+        if (!std::isfinite((double)g.inv[i])) return fail_arg("cell matrix is singular");
+    return DYNB_OK;
+}
+
+template <typename T>
+static int rg_suggest(int64_t N, const void* cell_host, const uint8_t* pbc_host, double radius, int64_t* src_cap,
+                      int64_t* cell_cap)
+{
+    Geom<T> g;
+    int rc = rg_geometry_checked<T>(cell_host, pbc_host, radius, g);
+    if (rc) return rc;
+    double full = 1.0, est = 1.0, ext[3] = {0, 0, 0};
+    for (int d = 0; d < 3; d++) {
+        double span = 1.0;
+        if (g.pbc[d]) {
+            full *= 2 * g.rep[d] + 1;
+            const double reach = g.rep[d] == 1 ? std::min(1.0, (double)g.cf[d]) : (double)g.rep[d];
+            est *= 1.0 + 2.0 * reach;
+            span = 1.0 + 2.0 * reach;
+        }
+        for (int k = 0; k < 3; k++) ext[k] += std::fabs((double)g.cell[3 * d + k]) * span;
+    }
+    const double nmax = (double)N * full;
+    double cap = std::min(nmax, (double)N * est * 1.25 + 4096.0);
+    if (cap < 1.0) cap = 1.0;
+    *src_cap = (int64_t)cap;
+    const double res = radius / 1.99;
+    double cells = 1.0;
+    for (int k = 0; k < 3; k++) cells *= std::ceil((ext[k] + 0.02) / res) + 1.0;
+    double ccap = std::min(cells * 1.02 + 64.0, std::max(8.0 * cap, 1048576.0));
+    ccap = std::min(ccap, 268435456.0);
+    *cell_cap = (int64_t)ccap;
+    return DYNB_OK;
+}
+
+template <typename T>
+static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const uint8_t* pbc_host, double radius,
+                   const int64_t* targets, int64_t Nt, void* ws, int64_t ws_bytes, int64_t src_cap, int64_t cell_cap,
+                   int32_t* counts_out, dynb_rg_header* header_host, cudaStream_t stream)
+{
+    Geom<T> g;
+    int rc = rg_geometry_checked<T>(cell_host, pbc_host, radius, g);
+    if (rc) return rc;
+    const int dtype = sizeof(T) == 8 ? DYNB_F64 : DYNB_F32;
+    const RgLayout L = rg_layout(N, Nt, src_cap, cell_cap, dtype);
+    if (ws_bytes < L.total) return fail_arg("workspace too small (see dynb_rg_workspace_bytes)");
+    unsigned char* w = static_cast<unsigned char*>(ws);
+    DevHeader* h = reinterpret_cast<DevHeader*>(w + L.hdr);
+
+    auto* posw = reinterpret_cast<Vec4<T>*>(w + L.posw);
+    auto* aff = reinterpret_cast<int4*>(w + L.aff);
+    auto* ccount = reinterpret_cast<uint32_t*>(w + L.ccount);
+    auto* cfill = reinterpret_cast<uint32_t*>(w + L.cfill);
+    auto* tccount = reinterpret_cast<uint32_t*>(w + L.tccount);
+    auto* tcfill = reinterpret_cast<uint32_t*>(w + L.tcfill);
+    auto* skey = reinterpret_cast<unsigned long long*>(w + L.skey);
+    auto* scell = reinterpret_cast<uint32_t*>(w + L.scell);
+    auto* spos = reinterpret_cast<Vec4<T>*>(w + L.spos);
+    auto* scode = reinterpret_cast<short4*>(w + L.scode);
+    auto* tkey = reinterpret_cast<uint32_t*>(w + L.tkey);
+    auto* tcell = reinterpret_cast<uint32_t*>(w + L.tcell);
+    auto* tpos = reinterpret_cast<Vec4<T>*>(w + L.tpos);
+    auto* tmeta = reinterpret_cast<int4*>(w + L.tmeta);
+    auto* tcount = reinterpret_cast<uint32_t*>(w + L.tcount);
+    auto* toffset = reinterpret_cast<long long*>(w + L.toffset);
+    auto* sums32 = reinterpret_cast<uint32_t*>(w + L.sums);
+    auto* sums64 = reinterpret_cast<long long*>(w + L.sums);
+    auto* params_dev = reinterpret_cast<PairParams<T>*>(w + L.hdr + RG_PARAMS_OFFSET);
+
+    static_assert(sizeof(DevHeader) <= RG_PARAMS_OFFSET, "header overlaps params");
+    static_assert(RG_PARAMS_OFFSET + sizeof(PairParams<T>) <= RG_HEADER_BYTES, "params overflow header block");
+    unsigned char init[RG_HEADER_BYTES];
+    memset(init, 0, sizeof(init));
+    {
+        DevHeader hi;
+        memset(&hi, 0, sizeof(hi));
+        for (int k = 0; k < 3; k++) { hi.bb_min[k] = ~0ull; hi.bb_max[k] = 0ull; }
+        memcpy(init, &hi, sizeof(hi));
+        PairParams<T> pp;
+        pp.h = h; pp.cstart = ccount; pp.tcstart = tccount; pp.spos = spos; pp.scode = scode; pp.tpos = tpos;
+        pp.tmeta = tmeta; pp.tcount = tcount; pp.toffset = toffset; pp.r2 = (T)radius * (T)radius;
+        memcpy(init + RG_PARAMS_OFFSET, &pp, sizeof(pp));
+    }
+    // Small pageable source: cudaMemcpyAsync stages it before returning, so the stack buffer may die.
+    DYNB_CUDA_OK(cudaMemcpyAsync(w + L.hdr, init, sizeof(init), cudaMemcpyHostToDevice, stream));
+    DYNB_CUDA_OK(cudaMemsetAsync(w + L.ccount, 0, (size_t)(L.posw - L.ccount), stream));
+    DYNB_CUDA_OK(cudaMemsetAsync(w + L.tcount, 0, (size_t)((Nt + 1) * 4), stream));
+    if (counts_out != nullptr && Nt > 0)
+        rg_zero_counts_kernel<<<(unsigned)((Nt + 255) / 256), 256, 0, stream>>>(Nt, counts_out);
+
+    const int vec_ok = (reinterpret_cast<uintptr_t>(pos_dev) % 16 == 0) ? 1 : 0;
+    rg_wrap_kernel<T><<<(unsigned)((N + WRAP_THREADS - 1) / WRAP_THREADS), WRAP_THREADS, 0, stream>>>(
+        static_cast<const T*>(pos_dev), N, g, vec_ok, posw, aff, h);
+    rg_grid_kernel<T><<<1, 32, 0, stream>>>(h, radius, (long long)src_cap, (long long)cell_cap);
+
+    const int64_t nb = std::max(N, Nt);
+    rg_bin_kernel<T, false><<<(unsigned)((nb + 255) / 256), 256, 0, stream>>>(
+        N, Nt, targets, g, posw, h, ccount, cfill, tccount, tcfill, skey, scell, tkey, tcell);
+    DYNB_CUDA_OK((exclusive_scan<uint32_t, uint32_t>(ccount, ccount, &h->ncell_plus1, cell_cap + 1, sums32, nullptr, stream)));
+    DYNB_CUDA_OK((exclusive_scan<uint32_t, uint32_t>(tccount, tccount, &h->ncell_plus1, cell_cap + 1, sums32, nullptr, stream)));
+    rg_bin_kernel<T, true><<<(unsigned)((nb + 255) / 256), 256, 0, stream>>>(
+        N, Nt, targets, g, posw, h, ccount, cfill, tccount, tcfill, skey, scell, tkey, tcell);
+    const int64_t nf = std::max(src_cap, Nt);
+    rg_bin_finalize_kernel<T><<<(unsigned)((nf + 255) / 256), 256, 0, stream>>>(
+        N, Nt, targets, g, posw, aff, h, ccount, tccount, skey, scell, tkey, tcell, spos, scode, tpos, tmeta);
+
+    const int smem = PAIR_WARPS * PAIR_WARP_BYTES;
+    DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_COUNT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    const int grid = sm_count_cached() * 4;
+    rg_pair_kernel<T, MODE_COUNT><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, nullptr, nullptr, nullptr, 0);
+    rg_post_count_kernel<T><<<(unsigned)((Nt + 255) / 256), 256, 0, stream>>>(Nt, tpos, tcount, counts_out, h);
+    DYNB_CUDA_OK((exclusive_scan<uint32_t, long long>(tcount, toffset, nullptr, Nt + 1, sums64,
+                                                       reinterpret_cast<long long*>(&h->E), stream)));
+    DYNB_CUDA_OK(cudaGetLastError());
+    if (header_host != nullptr)
+        DYNB_CUDA_OK(cudaMemcpyAsync(header_host, h, sizeof(dynb_rg_header), cudaMemcpyDeviceToHost, stream));
+    return DYNB_OK;
+}
+
+template <typename T>
+static int rg_fill(const void* ws, int64_t* ei, float* shifts, void* d2out, int64_t E, cudaStream_t stream)
+{
+    const unsigned char* w = static_cast<const unsigned char*>(ws);
+    const auto* params_dev = reinterpret_cast<const PairParams<T>*>(w + RG_PARAMS_OFFSET);
+    const int smem = PAIR_WARPS * PAIR_WARP_BYTES;
+    DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_FILL>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    const int grid = sm_count_cached() * 4;
+    rg_pair_kernel<T, MODE_FILL><<<grid, PAIR_THREADS, smem, stream>>>(
+        params_dev, reinterpret_cast<long long*>(ei), shifts, static_cast<T*>(d2out), (long long)E);
+    DYNB_CUDA_OK(cudaGetLastError());
+    return DYNB_OK;
+}
+
+}  // namespace dynb
+
+// ------------------------------------------------------------------------------------------
+// C ABI
+// ------------------------------------------------------------------------------------------
+using namespace dynb;
+
+extern "C" int dynb_rg_suggest_capacity(int64_t n_atoms, const void* cell_host, const uint8_t* pbc_host, double radius,
+                                        int dtype, int64_t* src_capacity, int64_t* cell_capacity)
+{
+    if (n_atoms < 0 || src_capacity == nullptr || cell_capacity == nullptr) return fail_arg("bad arguments");
+    if (dtype == DYNB_F32) return rg_suggest<float>(n_atoms, cell_host, pbc_host, radius, src_capacity, cell_capacity);
+    if (dtype == DYNB_F64) return rg_suggest<double>(n_atoms, cell_host, pbc_host, radius, src_capacity, cell_capacity);
+    return fail_arg("dtype must be DYNB_F32 or DYNB_F64");
+}
+
+extern "C" int dynb_rg_workspace_bytes(int64_t n_atoms, int64_t n_targets, int64_t src_capacity, int64_t cell_capacity,
+                                       int dtype, int64_t* bytes)
+{
+    if (n_atoms < 0 || n_targets < 0 || src_capacity < 1 || cell_capacity < 1 || bytes == nullptr)
+        return fail_arg("bad arguments");
+    if (dtype != DYNB_F32 && dtype != DYNB_F64) return fail_arg("dtype must be DYNB_F32 or DYNB_F64");
+    if (n_atoms >= (1ll << 31) || src_capacity >= (1ll << 31) || n_targets >= (1ll << 31) || cell_capacity >= (1ll << 31) - 8)
+        return fail_arg("sizes must stay below 2^31");
+    *bytes = rg_layout(n_atoms, n_targets, src_capacity, cell_capacity, dtype).total;
+    return DYNB_OK;
+}
+
+extern "C" int dynb_rg_plan(const void* pos_dev, int dtype, int64_t n_atoms, const void* cell_host,
+                            const uint8_t* pbc_host, double radius, const int64_t* target_indices_dev,
+                            int64_t n_targets, void* workspace_dev, int64_t workspace_bytes, int64_t src_capacity,
+                            int64_t cell_capacity, int32_t* neighbor_counts_dev, dynb_rg_header* header_host,
+                            void* stream)
+{
+    if (n_atoms <= 0 || n_targets <= 0) return fail_arg("n_atoms and n_targets must be positive (handle empty input in the caller)");
+    if (pos_dev == nullptr || workspace_dev == nullptr) return fail_arg("null device pointer");
+    if (target_indices_dev == nullptr && n_targets != n_atoms) return fail_arg("n_targets must equal n_atoms without target_indices");
+    if (src_capacity < 1 || cell_capacity < 1) return fail_arg("capacities must be positive");
+    if (n_atoms >= (1ll << 31) || src_capacity >= (1ll << 31) || n_targets >= (1ll << 31) || cell_capacity >= (1ll << 31) - 8)
+        return fail_arg("sizes must stay below 2^31");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == DYNB_F32)
+        return rg_plan<float>(pos_dev, n_atoms, cell_host, pbc_host, radius, target_indices_dev, n_targets, workspace_dev,
+                              workspace_bytes, src_capacity, cell_capacity, neighbor_counts_dev, header_host, s);
+    if (dtype == DYNB_F64)
+        return rg_plan<double>(pos_dev, n_atoms, cell_host, pbc_host, radius, target_indices_dev, n_targets, workspace_dev,
+                               workspace_bytes, src_capacity, cell_capacity, neighbor_counts_dev, header_host, s);
+    return fail_arg("dtype must be DYNB_F32 or DYNB_F64");
+}
+
+extern "C" int dynb_rg_fill(const void* workspace_dev, int dtype, int64_t* edge_index_dev, float* cell_shifts_dev,
+                            void* dist_sq_dev, int64_t E, void* stream)
+{
+    if (workspace_dev == nullptr) return fail_arg("null workspace");
+    if (E < 0) return fail_arg("E must be non-negative");
+    if (E == 0) return DYNB_OK;
+    if (edge_index_dev == nullptr || cell_shifts_dev == nullptr) return fail_arg("null output pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == DYNB_F32) return rg_fill<float>(workspace_dev, edge_index_dev, cell_shifts_dev, dist_sq_dev, E, s);
+    if (dtype == DYNB_F64) return rg_fill<double>(workspace_dev, edge_index_dev, cell_shifts_dev, dist_sq_dev, E, s);
+    return fail_arg("dtype must be DYNB_F32 or DYNB_F64");
+}

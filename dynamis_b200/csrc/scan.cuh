@@ -1,0 +1,126 @@
+// Device-wide exclusive prefix sum in three launches (tile sums, scan of the sums, apply).
+// No block ever waits on another block, so there is no spin-wait anywhere.
+//
+// The element count may live on the device (`n_dev`): cell grids are sized by a kernel, and
+// reading the count back would cost a host synchronisation.  `n_host` is then only the upper
+// bound that sizes the grid.  In-place operation (out == in) is allowed when the types match.
+#pragma once
+
+#include "common.cuh"
+
+namespace dynb {
+
+constexpr int SCAN_THREADS = 256;
+constexpr int SCAN_ITEMS = 8;
+constexpr int SCAN_TILE = SCAN_THREADS * SCAN_ITEMS;
+
+template <typename T>
+__device__ __forceinline__ T block_excl_scan(T v, T* block_total, T* warp_sums /* [SCAN_THREADS/32] */)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    T x = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        T y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
+    }
+    if (lane == 31) warp_sums[warp] = x;
+    __syncthreads();
+    T base = 0, tot = 0;
+#pragma unroll
+    for (int w = 0; w < SCAN_THREADS / 32; w++) {
+        T s = warp_sums[w];
+        if (w < warp) base += s;
+        tot += s;
+    }
+    __syncthreads();
+    *block_total = tot;
+    return base + x - v;
+}
+
+__device__ __forceinline__ int64_t scan_count(const uint32_t* n_dev, int64_t n_host)
+{
+    if (n_dev == nullptr) return n_host;
+    int64_t n = (int64_t)(*n_dev);
+    return n < n_host ? n : n_host;
+}
+
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(SCAN_THREADS)
+scan_tile_sums_kernel(const TIn* __restrict__ in, const uint32_t* __restrict__ n_dev, int64_t n_host,
+                      TOut* __restrict__ sums)
+{
+    __shared__ TOut warp_sums[SCAN_THREADS / 32];
+    const int64_t n = scan_count(n_dev, n_host);
+    const int64_t base = (int64_t)blockIdx.x * SCAN_TILE + (int64_t)threadIdx.x * SCAN_ITEMS;
+    TOut s = 0;
+#pragma unroll
+    for (int i = 0; i < SCAN_ITEMS; i++)
+        if (base + i < n) s += (TOut)in[base + i];
+    TOut tot;
+    (void)block_excl_scan<TOut>(s, &tot, warp_sums);
+    if (threadIdx.x == 0) sums[blockIdx.x] = tot;
+}
+
+// One block scans the tile sums in place (exclusive) and publishes the grand total.
+template <typename TOut>
+__global__ void __launch_bounds__(SCAN_THREADS)
+scan_sums_kernel(TOut* __restrict__ sums, int num_tiles, TOut* __restrict__ total_out)
+{
+    __shared__ TOut warp_sums[SCAN_THREADS / 32];
+    TOut carry = 0;
+    for (int b0 = 0; b0 < num_tiles; b0 += SCAN_THREADS) {
+        const int i = b0 + threadIdx.x;
+        TOut v = (i < num_tiles) ? sums[i] : (TOut)0;
+        TOut tot;
+        TOut ex = block_excl_scan<TOut>(v, &tot, warp_sums);
+        if (i < num_tiles) sums[i] = carry + ex;
+        carry += tot;
+    }
+    if (threadIdx.x == 0 && total_out != nullptr) *total_out = carry;
+}
+
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(SCAN_THREADS)
+scan_apply_kernel(const TIn* in, const uint32_t* __restrict__ n_dev, int64_t n_host,
+                  const TOut* __restrict__ sums, TOut* out)
+{
+    __shared__ TOut warp_sums[SCAN_THREADS / 32];
+    const int64_t n = scan_count(n_dev, n_host);
+    const int64_t base = (int64_t)blockIdx.x * SCAN_TILE + (int64_t)threadIdx.x * SCAN_ITEMS;
+    TOut v[SCAN_ITEMS];
+    TOut s = 0;
+#pragma unroll
+    for (int i = 0; i < SCAN_ITEMS; i++) {
+        v[i] = (base + i < n) ? (TOut)in[base + i] : (TOut)0;
+        s += v[i];
+    }
+    TOut tot;
+    TOut run = block_excl_scan<TOut>(s, &tot, warp_sums) + sums[blockIdx.x];
+#pragma unroll
+    for (int i = 0; i < SCAN_ITEMS; i++) {
+        if (base + i < n) out[base + i] = run;
+        run += v[i];
+    }
+}
+
+static inline int scan_num_tiles(int64_t n_host) { return (int)((n_host + SCAN_TILE - 1) / SCAN_TILE); }
+
+// `sums` must hold scan_num_tiles(n_host) elements of TOut.  `total_out` (device, may be null)
+// receives the sum of all elements.
+template <typename TIn, typename TOut>
+static inline cudaError_t exclusive_scan(const TIn* in, TOut* out, const uint32_t* n_dev, int64_t n_host,
+                                         TOut* sums, TOut* total_out, cudaStream_t stream)
+{
+    if (n_host <= 0) {
+        if (total_out) return cudaMemsetAsync(total_out, 0, sizeof(TOut), stream);
+        return cudaSuccess;
+    }
+    const int tiles = scan_num_tiles(n_host);
+    scan_tile_sums_kernel<TIn, TOut><<<tiles, SCAN_THREADS, 0, stream>>>(in, n_dev, n_host, sums);
+    scan_sums_kernel<TOut><<<1, SCAN_THREADS, 0, stream>>>(sums, tiles, total_out);
+    scan_apply_kernel<TIn, TOut><<<tiles, SCAN_THREADS, 0, stream>>>(in, n_dev, n_host, sums, out);
+    return cudaGetLastError();
+}
+
+}  // namespace dynb

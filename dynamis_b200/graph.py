@@ -1,0 +1,221 @@
+"""Periodic radius graph — host side of the reference's ``dynamis_state`` graph API.
+
+Same names, argument meaning and error behaviour as the reference's pybind entry points
+(dynamis_state/src/dynamis_state_bindings.cpp:153-163, 241-254; validation text from
+dynamis_state/src/csrc/graph/radius_graph.cpp:7-127) and its Python wrapper
+(dynamis_state/src/dynamis_state/radius_graph_pbc_cuda.py:13-110).  The work is done by the
+CUDA kernels behind ``dynb_rg_plan`` / ``dynb_rg_fill``; PyTorch only owns the memory and the
+stream.
+
+One extension: positions may be float64 (the reference rejects them); distances are then
+evaluated in float64.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+
+_STATE: dict = {}
+
+
+def _dev_state(device: torch.device) -> dict:
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    st = _STATE.get(key)
+    if st is None:
+        pinned = torch.empty(64, dtype=torch.uint8).pin_memory()
+        st = {"ws": None, "hdr_t": pinned, "hdr": _lib.RgHeader.from_address(pinned.data_ptr()), "geo": {}}
+        _STATE[key] = st
+    return st
+
+
+def _workspace(st: dict, nbytes: int, device: torch.device) -> torch.Tensor:
+    ws = st["ws"]
+    if ws is None or ws.numel() < nbytes:
+        st["ws"] = None
+        ws = torch.empty(int(nbytes * 1.1) + 4096, dtype=torch.uint8, device=device)
+        st["ws"] = ws
+    return ws
+
+
+def _validate(pos, cell, pbc, radius, max_num_neighbors, target_indices):
+    if not isinstance(pos, torch.Tensor) or not pos.is_cuda:
+        raise RuntimeError("pos must be a CUDA tensor")
+    if pos.dim() != 2 or pos.size(1) != 3:
+        got = ", ".join(str(s) for s in pos.shape)
+        raise RuntimeError(f"pos must have shape [N, 3], got [{got}]")
+    if pos.dtype not in (torch.float32, torch.float64):
+        raise RuntimeError(f"pos must be float32, got {pos.dtype}")
+    if cell.dim() != 2 or cell.size(0) != 3 or cell.size(1) != 3:
+        got = ", ".join(str(s) for s in cell.shape)
+        raise RuntimeError(f"cell must have shape [3, 3], got [{got}]")
+    if pbc.dim() != 1 or pbc.size(0) != 3:
+        raise RuntimeError(f"pbc must have shape [3], got [{pbc.size(0)}]")
+    if not (radius > 0.0):
+        raise RuntimeError(f"radius must be positive, got {radius}")
+    if max_num_neighbors < 0:
+        raise RuntimeError(f"max_num_neighbors must be non-negative, got {max_num_neighbors}")
+    if target_indices is not None:
+        if target_indices.device != pos.device:
+            raise RuntimeError("target_indices must be on the same device as pos")
+        if target_indices.dim() != 1:
+            raise RuntimeError(f"target_indices must be 1-D, got shape {list(target_indices.shape)}")
+        if target_indices.dtype != torch.int64:
+            raise RuntimeError(f"target_indices must be int64, got {target_indices.dtype}")
+
+
+def _empty_result(pos, n_target):
+    dev = pos.device
+    return (
+        torch.empty((2, 0), dtype=torch.int64, device=dev),
+        torch.empty((0, 3), dtype=torch.float32, device=dev),
+        torch.zeros((1,), dtype=torch.int64, device=dev),
+        torch.zeros((n_target,), dtype=torch.int32, device=dev),
+    )
+
+
+def _graph_impl(pos, cell, pbc, radius, target_indices, counts_only, want_dist_sq=False):
+    """Shared implementation.  Returns (edge_index, cell_shifts, num_neighbors_image,
+    neighbor_counts[, dist_sq])."""
+    pos = pos.contiguous()
+    N = pos.size(0)
+    if target_indices is not None:
+        target_indices = target_indices.contiguous()
+        Nt = target_indices.size(0)
+    else:
+        Nt = N
+    if N == 0 or Nt == 0:  # reference: radius_graph_kernels.cu:499-509
+        out = _empty_result(pos, Nt)
+        return out + ((torch.empty(0, dtype=pos.dtype, device=pos.device),) if want_dist_sq else ())
+
+    L = _lib.lib()
+    dev = pos.device
+    dtype_code = _lib.DYNB_F64 if pos.dtype == torch.float64 else _lib.DYNB_F32
+    np_real = np.float64 if pos.dtype == torch.float64 else np.float32
+    cell_h = np.ascontiguousarray(cell.detach().to("cpu").numpy().astype(np_real))
+    pbc_h = np.ascontiguousarray(pbc.detach().to("cpu").numpy().astype(bool).astype(np.uint8))
+    radius = float(np.float32(radius)) if dtype_code == _lib.DYNB_F32 else float(radius)
+
+    with torch.cuda.device(dev):
+        st = _dev_state(dev)
+        src_cap = ctypes.c_int64()
+        cell_cap = ctypes.c_int64()
+        _lib.check(L.dynb_rg_suggest_capacity(N, cell_h.ctypes.data, pbc_h.ctypes.data, radius, dtype_code,
+                                              ctypes.byref(src_cap), ctypes.byref(cell_cap)), "rg_suggest_capacity")
+        src_cap, cell_cap = src_cap.value, cell_cap.value
+        counts = torch.empty((Nt,), dtype=torch.int32, device=dev)
+        stream = torch.cuda.current_stream(dev)
+        hdr = st["hdr"]
+        for attempt in range(3):
+            nbytes = ctypes.c_int64()
+            _lib.check(L.dynb_rg_workspace_bytes(N, Nt, src_cap, cell_cap, dtype_code, ctypes.byref(nbytes)),
+                       "rg_workspace_bytes")
+            ws = _workspace(st, nbytes.value, dev)
+            _lib.check(L.dynb_rg_plan(pos.data_ptr(), dtype_code, N, cell_h.ctypes.data, pbc_h.ctypes.data, radius,
+                                      target_indices.data_ptr() if target_indices is not None else None, Nt,
+                                      ws.data_ptr(), ws.numel(), src_cap, cell_cap, counts.data_ptr(),
+                                      st["hdr_t"].data_ptr(), stream.cuda_stream), "rg_plan")
+            stream.synchronize()
+            status = int(hdr.status)
+            if status & _lib.RG_SRC_OVERFLOW and attempt < 2:
+                src_cap = int(hdr.M) + 1024
+                continue
+            break
+        if status & _lib.RG_BAD_TARGET:
+            raise RuntimeError("target_indices contains an index outside [0, N)")
+        if status & _lib.RG_NONFINITE:
+            raise RuntimeError("pos contains NaN or Inf")
+        if status & _lib.RG_SHIFT_RANGE:
+            raise RuntimeError("an atom lies too many periodic cells outside the unit cell (limit 32767)")
+        if status & _lib.RG_SRC_OVERFLOW:
+            raise RuntimeError("periodic-image capacity overflow")
+        E = int(hdr.E)
+        if counts_only or E == 0:
+            out = (
+                torch.empty((2, 0), dtype=torch.int64, device=dev),
+                torch.empty((0, 3), dtype=torch.float32, device=dev),
+                torch.zeros((1,), dtype=torch.int64, device=dev),
+                counts,
+            )
+            return out + ((torch.empty(0, dtype=pos.dtype, device=dev),) if want_dist_sq else ())
+        edge_index = torch.empty((2, E), dtype=torch.int64, device=dev)
+        shifts = torch.empty((E, 3), dtype=torch.float32, device=dev)
+        d2 = torch.empty((E,), dtype=pos.dtype, device=dev) if want_dist_sq else None
+        _lib.check(L.dynb_rg_fill(ws.data_ptr(), dtype_code, edge_index.data_ptr(), shifts.data_ptr(),
+                                  d2.data_ptr() if d2 is not None else None, E, stream.cuda_stream), "rg_fill")
+        nni = torch.full((1,), E, dtype=torch.int64, device=dev)
+    out = (edge_index, shifts, nni, counts)
+    return out + ((d2,) if want_dist_sq else ())
+
+
+def radius_graph_pbc(pos, cell, pbc, radius, max_num_neighbors, enforce_max_strictly):
+    """(edge_index [2,E] int64, cell_shifts [E,3] float32, num_neighbors_image [1] int64).
+
+    edge_index row 0 is the neighbour (source), row 1 the centre (target);
+    ``pos[src] + cell_shifts @ cell - pos[dst]`` is the edge vector.  ``max_num_neighbors`` and
+    ``enforce_max_strictly`` are accepted and ignored, as in the reference
+    (radius_graph_kernels.cu:771-775): every neighbour inside the cutoff is returned.
+    """
+    _validate(pos, cell, pbc, float(radius), int(max_num_neighbors), None)
+    ei, cs, nni, _ = _graph_impl(pos, cell, pbc, float(radius), None, False)
+    return ei, cs, nni
+
+
+def radius_graph_pbc_ex(pos, cell, pbc, radius, max_num_neighbors, enforce_max_strictly,
+                        target_indices: Optional[torch.Tensor] = None):
+    """As radius_graph_pbc, restricted to edges whose centre is in ``target_indices`` (sources stay
+    all atoms), plus ``neighbor_counts [N_target] int32`` in the order of ``target_indices``."""
+    _validate(pos, cell, pbc, float(radius), int(max_num_neighbors), target_indices)
+    return _graph_impl(pos, cell, pbc, float(radius), target_indices, False)
+
+
+def radius_graph_pbc_counts_ex(pos, cell, pbc, radius, target_indices: Optional[torch.Tensor] = None):
+    """Per-target degrees only (no edge buffers, no fill pass)."""
+    _validate(pos, cell, pbc, float(radius), 0, target_indices)
+    return _graph_impl(pos, cell, pbc, float(radius), target_indices, True)[3]
+
+
+def radius_graph_pbc_with_dist(pos, cell, pbc, radius, target_indices: Optional[torch.Tensor] = None):
+    """Extension: also returns the squared edge lengths the kernel evaluated (dtype of ``pos``)."""
+    _validate(pos, cell, pbc, float(radius), 0, target_indices)
+    return _graph_impl(pos, cell, pbc, float(radius), target_indices, False, want_dist_sq=True)
+
+
+def radius_graph_pbc_cuda(data, radius: float, max_num_neighbors_threshold: int,
+                          enforce_max_neighbors_strictly: bool = False, pbc: Optional[torch.Tensor] = None):
+    """Batch-object wrapper (``data.pos``, ``data.cell [B,3,3]``, ``data.natoms [B]``, ``data.pbc``)."""
+    if pbc is None:
+        data_pbc = torch.atleast_2d(data.pbc)
+        all_true = torch.all(data_pbc, dim=0)
+        all_false = torch.all(~data_pbc, dim=0)
+        if (~(all_true | all_false)).any():
+            raise RuntimeError(
+                "Different structures in the batch have different PBC "
+                "configurations. This is not currently supported."
+            )
+        pbc_flags = all_true
+    else:
+        pbc_flags = pbc.to(torch.bool)
+
+    batch_size = len(data.natoms)
+    if batch_size == 1:
+        return radius_graph_pbc(data.pos, data.cell[0], pbc_flags, float(radius),
+                                int(max_num_neighbors_threshold), enforce_max_neighbors_strictly)
+    eis, cos, nns = [], [], []
+    natoms = [int(n) for n in data.natoms.tolist()]
+    off = 0
+    for i, n in enumerate(natoms):
+        ei, co, nn = radius_graph_pbc(data.pos[off:off + n], data.cell[i], pbc_flags, float(radius),
+                                      int(max_num_neighbors_threshold), enforce_max_neighbors_strictly)
+        if ei.size(1) > 0:
+            ei = ei + off
+        eis.append(ei)
+        cos.append(co)
+        nns.append(nn)
+        off += n
+    return torch.cat(eis, dim=1), torch.cat(cos, dim=0), torch.cat(nns, dim=0)
