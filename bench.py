@@ -1,0 +1,317 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: periodic radius graph (+ Morton partition, + halo exchange when N > 1).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N > 1 is launched by torchrun (one rank per GPU, NCCL).  Prints ONE JSON line on rank 0.
+
+A "step" is one pass of the path over one batch of synthetic input:
+  N = 1   the 1,000,000-atom random liquid (density 0.1 atoms/Å^3, L = 215.4 Å, fp32, r = 5 Å):
+          Morton-key partition + radius graph (edge_index, shifts, degrees).
+  N > 1   the same liquid with N x 1,000,000 atoms, cut into N subdomains along the Morton curve;
+          every rank exchanges halo positions, builds the graph of its own atoms over
+          [owned | halo], then exchanges two layers of 128-wide node embeddings forward and the
+          force gradients backward (weak scaling: per-GPU work is fixed).
+
+value       whole-job edges/s with inputs resident in HBM, CUDA-event time, max over ranks.
+e2e         the same through the public API with the positions arriving from pinned host memory
+            and the degrees + edge count read back every step (wall clock around the K steps).
+roofline    the dominant kernel (the edge-writing pass of the cell scan) timed alone, against the
+            measured HBM copy bandwidth of MEASURED_PEAKS.json.
+cpu_baseline / --impl reference
+            the CPU restatement of the reference's algorithm (oracle/, OpenMP over all host
+            threads) on the same workload; the reference itself has no CPU radius-graph path.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ATOMS_PER_GPU = 1_000_000
+DENSITY = 0.1
+RADIUS = 5.0
+SEED = 1002
+
+
+def _peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.perf_counter(), line.strip()))
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.samples:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm, smx = float(parts[0]), float(parts[1])
+            except ValueError:
+                continue
+            mx = smx
+            if t0 - 0.05 <= ts <= t1 + 0.15:
+                mhz.append(sm)
+                for nm, v in zip(names, parts[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(nm)
+        if not mhz:
+            mhz = [float(l.split(",")[0]) for _, l in self.samples[-3:] if l and l.split(",")[0].strip().replace(".", "").isdigit()]
+        return {"sm_mhz": float(np.median(mhz)) if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons)}
+
+
+def liquid(n_atoms: int):
+    from dynamis_b200 import synthetic
+
+    return synthetic.random_liquid(n_atoms, density=DENSITY, seed=SEED, radius=RADIUS)
+
+
+def cpu_baseline(sample_atoms: int, steps: int = 1):
+    """Oracle (CPU port of the reference algorithm) on a liquid of `sample_atoms` atoms, all host threads."""
+    from oracle import cpu_oracle as O
+
+    pos, cell, pbc, r = liquid(sample_atoms)
+    threads = O.max_threads()
+    best = None
+    E = 0
+    for _ in range(max(1, steps)):
+        t = time.perf_counter()
+        g = O.radius_graph(pos, cell, pbc, r)
+        dt = time.perf_counter() - t
+        E = g["E"]
+        best = dt if best is None else min(best, dt)
+    return {"value": E / best, "unit": "edges/s", "cores": threads, "kind": "port",
+            "sample": f"{sample_atoms} atoms of the same liquid (density {DENSITY}, r = {RADIUS}), {E} edges, best of {max(1, steps)}"}, best
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = 250_000
+    base, _ = cpu_baseline(sample, steps=1)  # warm-up (page in, build)
+    from oracle import cpu_oracle as O
+
+    pos, cell, pbc, r = liquid(sample)
+    for _ in range(min(args.warmup, 2)):
+        O.radius_graph(pos, cell, pbc, r)
+    t0 = time.perf_counter()
+    E = 0
+    for _ in range(args.steps):
+        E = O.radius_graph(pos, cell, pbc, r)["E"]
+    dt = time.perf_counter() - t0
+    v = E * args.steps / dt
+    line = {
+        "impl": "reference", "metric": "radius_graph_edges_per_s", "value": v, "unit": "edges/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "random liquid 1,000,000 atoms/GPU, density 0.1, r=5.0, fp32 (configs[1]); "
+                               f"CPU arm timed on a {sample}-atom sample of it"},
+        "cpu_baseline": {"value": v, "unit": "edges/s", "cores": base["cores"], "kind": "port",
+                         "sample": f"{sample}-atom liquid, {E} edges per step"},
+        "e2e": {"value": v, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "the reference has no CPU radius-graph path; this is the CPU port of its algorithm (oracle/)",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+
+    import dynamis_b200 as D
+    from dynamis_b200 import graph as G
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    if world > 1:
+        from dynamis_b200 import bench_multi
+
+        return bench_multi.run(args, rank, world, dev)
+
+    K, W = args.steps, max(args.warmup, 3)
+    pos_np, cell_np, pbc_np, r = liquid(ATOMS_PER_GPU)
+    N = pos_np.shape[0]
+    pos_pin = torch.from_numpy(pos_np).pin_memory()
+    pos = pos_pin.to(dev)
+    cell = torch.from_numpy(cell_np)
+    pbc = torch.from_numpy(pbc_np)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    have_sfc = hasattr(D, "sfc_partition_labels")
+
+    def step(p):
+        labels = D.sfc_partition_labels(p, None, 8, 0) if have_sfc else None
+        out = D.radius_graph_pbc_ex(p, cell, pbc, r, 0, False)
+        return out, labels
+
+    for _ in range(W):
+        out, _ = step(pos)
+    E = int(out[2].item())
+    del out
+    torch.cuda.synchronize()
+
+    # ---- device-resident throughput: per-step CUDA events, L2 flushed between steps
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.25)
+    t_wall0 = time.perf_counter()
+    total_ms = 0.0
+    for _ in range(K):
+        flush.zero_()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        out, _ = step(pos)
+        b.record()
+        torch.cuda.synchronize()
+        total_ms += a.elapsed_time(b)
+        del out
+    t_wall1 = time.perf_counter()
+    clocks = sampler.stop(t_wall0, t_wall1)
+    ms_per_step = total_ms / K
+    value = E / (ms_per_step * 1e-3)
+
+    # ---- end to end: positions from pinned host memory, degrees + edge count back to the host
+    counts_pin = torch.empty(N, dtype=torch.int32).pin_memory()
+    nni_pin = torch.empty(1, dtype=torch.int64).pin_memory()
+    pos_in = torch.empty_like(pos)
+    for _ in range(2):
+        pos_in.copy_(pos_pin, non_blocking=True)
+        out, _ = step(pos_in)
+        counts_pin.copy_(out[3], non_blocking=True)
+        nni_pin.copy_(out[2], non_blocking=True)
+        torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        pos_in.copy_(pos_pin, non_blocking=True)
+        out, _ = step(pos_in)
+        counts_pin.copy_(out[3], non_blocking=True)
+        nni_pin.copy_(out[2], non_blocking=True)
+        torch.cuda.synchronize()
+        del out
+    e2e_s = (time.perf_counter() - t0) / K
+    assert int(nni_pin.item()) == E
+    e2e = {"value": E / e2e_s, "unit": "edges/s", "ms_per_step": e2e_s * 1e3,
+           "h2d_bytes_per_step": int(pos_pin.numel() * 4), "d2h_bytes_per_step": int(N * 4 + 8)}
+
+    # ---- the dominant kernel alone (edge-writing pass), CUDA events on its stream, L2 flushed
+    plan = G.plan_radius_graph(pos, cell, pbc, r)
+    ei = torch.empty((2, plan.E), dtype=torch.int64, device=dev)
+    sh = torch.empty((plan.E, 3), dtype=torch.float32, device=dev)
+    for _ in range(3):
+        plan.fill_into(ei, sh)
+    torch.cuda.synchronize()
+    kt = []
+    for _ in range(max(K, 10)):
+        flush.zero_()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        plan.fill_into(ei, sh)
+        b.record()
+        torch.cuda.synchronize()
+        kt.append(a.elapsed_time(b))
+    fill_ms = float(np.mean(kt))
+    peak, peak_kind = _peaks()
+    alg_bytes = 28.0 * plan.E
+    achieved = alg_bytes / (fill_ms * 1e-3) / 1e9
+    traffic = None
+    tp = os.path.join(ROOT, "profiles", "rg_pair_fill_traffic.json")
+    if os.path.exists(tp):
+        with open(tp) as f:
+            tj = json.load(f)
+        traffic = tj["dram_bytes_per_edge"] * plan.E
+    roofline = {"bound": "hbm", "kernel": "rg_pair_kernel<float, FILL>", "achieved": achieved, "peak": peak,
+                "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": traffic,
+                "algorithmic_bytes": alg_bytes, "ms_per_launch": fill_ms}
+    del ei, sh
+
+    base, _ = cpu_baseline(ATOMS_PER_GPU, steps=1)
+
+    line = {
+        "metric": "radius_graph_edges_per_s", "value": value, "unit": "edges/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "random liquid 1,000,000 atoms, density 0.1 atoms/A^3, cubic periodic box L=215.4 A, fp32, "
+                               "cutoff 5.0 A (configs[1]): " + ("Morton partition + " if have_sfc else "") + "radius graph",
+                   "edges_per_step": E, "l2": "256 MiB buffer written between timed steps; a step itself writes 1.5 GB"},
+        "roofline": roofline, "cpu_baseline": base, "e2e": e2e, "clocks": clocks,
+        "gpu_launches": D.launches_per_graph() + (D.launches_per_partition() if have_sfc else 0),
+        "halo_exchange_ms_per_step": None,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
