@@ -14,3 +14,19 @@ from .graph import (  # noqa: F401
     radius_graph_pbc_ex,
     radius_graph_pbc_with_dist,
 )
+from .halo import extract_halo_info, filter_edges_to_radius  # noqa: F401
+from .partition import (  # noqa: F401
+    SFCCurveType,
+    SFCPartitioner,
+    SimpleSpatialPartitioner,
+    launches_per_partition,
+    sfc_keys,
+    sfc_partition_labels,
+)
+from .state import (  # noqa: F401
+    DistEnvironment,
+    DynamisState,
+    MolecularInfo,
+    PartitionMessagePassingInfo,
+    SimulationConfig,
+)

@@ -47,6 +47,23 @@ SIGNATURES = {
     "dynb_rg_workspace_bytes": (_i32, [_i64, _i64, _i64, _i64, _i32, ctypes.POINTER(_i64)]),
     "dynb_rg_plan": (_i32, [_p, _i32, _i64, _p, _p, _f64, _p, _i64, _p, _i64, _i64, _i64, _p, _p, _p]),
     "dynb_rg_fill": (_i32, [_p, _i32, _p, _p, _p, _i64, _p]),
+    "dynb_rg_halo_mark": (_i32, [_p, _i32, _p, _i64, _i64, _p, _p, _p]),
+    "dynb_sfc_workspace_bytes": (_i32, [_i64, ctypes.POINTER(_i64)]),
+    "dynb_sfc_partition": (_i32, [_p, _i64, _p, _i64, _i32, _p, _p, _p, _i64, _p]),
+    "dynb_sfc_keys": (_i32, [_p, _i64, _i32, _p, _p, _i64, _p]),
+    "dynb_radix_sort_workspace_bytes": (_i32, [_i64, ctypes.POINTER(_i64)]),
+    "dynb_radix_sort_pairs": (_i32, [_p, _p, _i64, _i32, _i32, _p, _i64, _p]),
+    "dynb_bincount_i64": (_i32, [_p, _i64, _i64, _p, _p, _p]),
+    "dynb_select_workspace_bytes": (_i32, [_i64, ctypes.POINTER(_i64)]),
+    "dynb_select_eq_i64": (_i32, [_p, _i64, _i64, _p, _p, _p, _p, _i64, _p]),
+    "dynb_halo_mark_from_edges": (_i32, [_p, _i64, _p, _i64, _i64, _i64, _p, _p, _p, _p, _p]),
+    "dynb_csr_workspace_bytes": (_i32, [_i64, _i64, ctypes.POINTER(_i64)]),
+    "dynb_csr_plan": (_i32, [_p, _p, _i64, _i64, _i32, _i64, _p, _p, _i64, _p]),
+    "dynb_csr_fill": (_i32, [_p, _p, _i64, _i64, _i32, _i64, _p, _p, _p, _p, _p]),
+    "dynb_gather_not_u8": (_i32, [_p, _p, _i64, _p, _p]),
+    "dynb_scatter_iota": (_i32, [_p, _i64, _i64, _p, _p, _p]),
+    "dynb_filter_edges_plan": (_i32, [_p, _p, _p, _p, _f64, _i64, _p, _p, _i64, _p]),
+    "dynb_filter_edges_fill": (_i32, [_p, _p, _i32, _i64, _i64, _p, _p, _p, _p]),
 }
 
 _LIB = None

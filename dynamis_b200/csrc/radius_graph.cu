@@ -422,7 +422,18 @@ constexpr int PAIR_CAND_BYTES = 6144;  // dense candidate list per warp
 constexpr int PAIR_LIST = 128;         // parked hits per warp
 constexpr int PAIR_WARP_BYTES = PAIR_CAND_BYTES + PAIR_LIST * 2;
 
-enum { MODE_COUNT = 0, MODE_FILL = 1 };
+enum { MODE_COUNT = 0, MODE_FILL = 1, MODE_HALO = 2 };
+
+// MODE_HALO: instead of counting or writing edges, record for every edge src -> dst whose
+// endpoints have different owners that owner(dst) needs src (bit owner(dst) of needed[src]) and
+// that dst has a foreign neighbour.  This is the edge loop of the reference's halo-map builder
+// (dynamis_state/src/csrc/build_halo_maps.cpp:50-58, 127-138) without materialising the graph.
+struct HaloArgs {
+    const long long* owner;   // [n_atoms] rank of each atom
+    uint32_t* needed;         // [n_atoms, words]
+    unsigned char* has_foreign;  // [n_atoms]
+    int words;
+};
 
 template <typename T> struct PairParams {
     const DevHeader* h;
@@ -444,7 +455,7 @@ constexpr int64_t RG_HEADER_BYTES = 1024;
 template <typename T, int MODE>
 __global__ void __launch_bounds__(PAIR_THREADS)
 rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restrict__ ei, float* __restrict__ shifts,
-               T* __restrict__ d2out, const long long E)
+               T* __restrict__ d2out, const long long E, const HaloArgs halo)
 {
     const PairParams<T> p = *params_dev;
     extern __shared__ __align__(32) unsigned char smem_raw[];
@@ -506,7 +517,7 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                 if (j < clen) {
                     const int gidx = ra + (jj - ro);
                     c = p.spos[gidx];
-                    c.w = bits_to_real((int32_t)gidx, T());
+                    if (MODE == MODE_FILL) c.w = bits_to_real((int32_t)gidx, T());
                 } else {
                     c.x = c.y = c.z = (T)3.0e38f;  // never within the cutoff
                     c.w = (T)0;
@@ -518,13 +529,19 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
             for (uint32_t t = t0; t < t1; t++) {
                 const Vec4<T> tp = p.tpos[t];
                 const T tx = tp.x, ty = tp.y, tz = tp.z;
-                int produced = (chunk == 0) ? 0 : (int)p.tcount[t];
+                int produced = (chunk == 0 || MODE == MODE_HALO) ? 0 : (int)p.tcount[t];
                 int cnt = 0;
                 int4 tm;
                 long long base = 0;
+                long long owner_t = 0;
+                bool foreign = false;
                 if (MODE == MODE_FILL) {
                     tm = p.tmeta[t];
                     base = p.toffset[t];
+                }
+                if (MODE == MODE_HALO) {
+                    tm = p.tmeta[t];
+                    owner_t = halo.owner[tm.x];
                 }
                 for (int k = 0; k < clen32; k += 32) {
                     const int j = k + lane;
@@ -537,6 +554,17 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                         if (hit) list[cnt + __popc(mask & lt)] = (unsigned short)j;
                     }
                     cnt += __popc(mask);
+                    if (MODE == MODE_HALO) {
+                        if (hit) {
+                            const int a = real_to_bits(c.w);
+                            if (halo.owner[a] != owner_t) {
+                                uint32_t* wd = &halo.needed[(long long)a * halo.words + (owner_t >> 5)];
+                                const uint32_t bit = 1u << (owner_t & 31);
+                                if (!(*wd & bit)) atomicOr(wd, bit);
+                                foreign = true;
+                            }
+                        }
+                    }
                     if (MODE == MODE_FILL) {
                         if (cnt > PAIR_LIST - 32 || k + 32 >= clen32) {
                             __syncwarp();
@@ -565,8 +593,10 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                 }
                 if (MODE == MODE_COUNT) {
                     if (lane == 0) p.tcount[t] = (uint32_t)(produced + cnt);
-                } else {
+                } else if (MODE == MODE_FILL) {
                     if (lane == 0 && cbeg + CAP < L) p.tcount[t] = (uint32_t)produced;
+                } else {
+                    if (__any_sync(0xffffffffu, foreign) && lane == 0) halo.has_foreign[tm.x] = 1;
                 }
             }
         }
@@ -798,7 +828,7 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
     const int smem = PAIR_WARPS * PAIR_WARP_BYTES;
     DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_COUNT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int grid = sm_count_cached() * 4;
-    rg_pair_kernel<T, MODE_COUNT><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, nullptr, nullptr, nullptr, 0);
+    rg_pair_kernel<T, MODE_COUNT><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, nullptr, nullptr, nullptr, 0, HaloArgs{});
     rg_post_count_kernel<T><<<(unsigned)((Nt + 255) / 256), 256, 0, stream>>>(Nt, tpos, tcount, counts_out, h);
     DYNB_CUDA_OK((exclusive_scan<uint32_t, long long>(tcount, toffset, nullptr, Nt + 1, sums64,
                                                        reinterpret_cast<long long*>(&h->E), stream)));
@@ -817,7 +847,20 @@ static int rg_fill(const void* ws, int64_t* ei, float* shifts, void* d2out, int6
     DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_FILL>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int grid = sm_count_cached() * 4;
     rg_pair_kernel<T, MODE_FILL><<<grid, PAIR_THREADS, smem, stream>>>(
-        params_dev, reinterpret_cast<long long*>(ei), shifts, static_cast<T*>(d2out), (long long)E);
+        params_dev, reinterpret_cast<long long*>(ei), shifts, static_cast<T*>(d2out), (long long)E, HaloArgs{});
+    DYNB_CUDA_OK(cudaGetLastError());
+    return DYNB_OK;
+}
+
+template <typename T>
+static int rg_halo_mark(const void* ws, const HaloArgs& ha, cudaStream_t stream)
+{
+    const unsigned char* w = static_cast<const unsigned char*>(ws);
+    const auto* params_dev = reinterpret_cast<const PairParams<T>*>(w + RG_PARAMS_OFFSET);
+    const int smem = PAIR_WARPS * PAIR_WARP_BYTES;
+    DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_HALO>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    const int grid = sm_count_cached() * 4;
+    rg_pair_kernel<T, MODE_HALO><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, nullptr, nullptr, nullptr, 0, ha);
     DYNB_CUDA_OK(cudaGetLastError());
     return DYNB_OK;
 }
@@ -882,5 +925,24 @@ extern "C" int dynb_rg_fill(const void* workspace_dev, int dtype, int64_t* edge_
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (dtype == DYNB_F32) return rg_fill<float>(workspace_dev, edge_index_dev, cell_shifts_dev, dist_sq_dev, E, s);
     if (dtype == DYNB_F64) return rg_fill<double>(workspace_dev, edge_index_dev, cell_shifts_dev, dist_sq_dev, E, s);
+    return fail_arg("dtype must be DYNB_F32 or DYNB_F64");
+}
+
+extern "C" int dynb_rg_halo_mark(const void* workspace_dev, int dtype, const int64_t* owner_dev, int64_t n_atoms,
+                                 int64_t world_size, uint32_t* needed_dev, uint8_t* has_foreign_dev, void* stream)
+{
+    if (workspace_dev == nullptr || owner_dev == nullptr || needed_dev == nullptr || has_foreign_dev == nullptr)
+        return fail_arg("null pointer");
+    if (n_atoms <= 0 || world_size < 1) return fail_arg("bad sizes");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    HaloArgs ha;
+    ha.owner = reinterpret_cast<const long long*>(owner_dev);
+    ha.needed = needed_dev;
+    ha.has_foreign = has_foreign_dev;
+    ha.words = (int)((world_size + 31) / 32);
+    DYNB_CUDA_OK(cudaMemsetAsync(needed_dev, 0, (size_t)n_atoms * ha.words * 4, s));
+    DYNB_CUDA_OK(cudaMemsetAsync(has_foreign_dev, 0, (size_t)n_atoms, s));
+    if (dtype == DYNB_F32) return rg_halo_mark<float>(workspace_dev, ha, s);
+    if (dtype == DYNB_F64) return rg_halo_mark<double>(workspace_dev, ha, s);
     return fail_arg("dtype must be DYNB_F32 or DYNB_F64");
 }

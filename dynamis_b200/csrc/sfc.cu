@@ -1,0 +1,412 @@
+// Space-filling-curve partition for B200 (sm_100a): bounds -> keys -> stable LSD radix sort ->
+// contiguous split into W ranks.
+//
+// Replaces sfc_partition_cuda_impl (dynamis_state/src/csrc/partition/sfc_kernels.cu:178-251) and
+// its kernels (:32-173).  The key arithmetic (IEEE division by the range, truncating quantisation,
+// 21-bit Morton interleave, the 7-iteration bit transform the reference calls "Hilbert") is kept
+// expression for expression; the sort is ours: a stable least-significant-digit radix sort on
+// 8-bit digits of (key, atom index) pairs, so that atoms with equal keys keep ascending index order
+// (the reference's at::sort leaves that order unspecified).
+
+#include "common.cuh"
+#include "scan.cuh"
+
+namespace dynb {
+
+// ------------------------------------------------------------------------------------------ bounds
+struct SfcBounds {
+    uint32_t mn[3];  // ordered-integer images
+    uint32_t mx[3];
+    float pmin[3];
+    float prange[3];
+};
+
+__global__ void __launch_bounds__(256)
+sfc_minmax_kernel(const float* __restrict__ pos, int64_t n, SfcBounds* __restrict__ b)
+{
+    uint32_t mn[3] = {0xffffffffu, 0xffffffffu, 0xffffffffu}, mx[3] = {0u, 0u, 0u};
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            const uint32_t o = ordered_u32(pos[3 * i + k]);
+            mn[k] = min(mn[k], o);
+            mx[k] = max(mx[k], o);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            mn[k] = min(mn[k], __shfl_xor_sync(0xffffffffu, mn[k], o));
+            mx[k] = max(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], o));
+        }
+    if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            atomicMin(&b->mn[k], mn[k]);
+            atomicMax(&b->mx[k], mx[k]);
+        }
+    }
+}
+
+__global__ void sfc_bounds_finish_kernel(SfcBounds* b)
+{
+    const int k = threadIdx.x;
+    if (k < 3) {
+        const float lo = unordered_f32(b->mn[k]), hi = unordered_f32(b->mx[k]);
+        float range = hi - lo;                       // sfc_kernels.cu:197-198
+        b->pmin[k] = lo;
+        b->prange[k] = (range > 0.0f) ? range : 1.0f;
+    }
+}
+
+// ------------------------------------------------------------------------------------------ keys
+__device__ __forceinline__ uint64_t spread_bits_21(uint32_t v)
+{
+    uint64_t x = v & 0x1FFFFF;
+    x = (x | (x << 32)) & 0x1F00000000FFFFULL;
+    x = (x | (x << 16)) & 0x1F0000FF0000FFULL;
+    x = (x | (x << 8)) & 0x100F00F00F00F00FULL;
+    x = (x | (x << 4)) & 0x10C30C30C30C30C3ULL;
+    x = (x | (x << 2)) & 0x1249249249249249ULL;
+    return x;
+}
+
+template <int CURVE>
+__global__ void __launch_bounds__(256)
+sfc_keys_kernel(const float* __restrict__ pos, int64_t n, const SfcBounds* __restrict__ b,
+                uint64_t* __restrict__ keys, uint32_t* __restrict__ idx)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float nx = (pos[i * 3 + 0] - b->pmin[0]) / b->prange[0];
+    const float ny = (pos[i * 3 + 1] - b->pmin[1]) / b->prange[1];
+    const float nz = (pos[i * 3 + 2] - b->pmin[2]) / b->prange[2];
+    uint64_t key;
+    if (CURVE == 0) {
+        const uint32_t grid_max = (1u << 21) - 1;
+        const uint32_t ix = min((uint32_t)(nx * grid_max), grid_max);
+        const uint32_t iy = min((uint32_t)(ny * grid_max), grid_max);
+        const uint32_t iz = min((uint32_t)(nz * grid_max), grid_max);
+        key = spread_bits_21(ix) | (spread_bits_21(iy) << 1) | (spread_bits_21(iz) << 2);
+    } else {
+        const int order = 7;
+        const int grid_max = (1 << order) - 1;
+        const int x = min(max((int)(nx * grid_max), 0), grid_max);
+        const int y = min(max((int)(ny * grid_max), 0), grid_max);
+        const int z = min(max((int)(nz * grid_max), 0), grid_max);
+        long long result = 0;
+#pragma unroll
+        for (int bit = 0; bit < order; bit++) {
+            const int xb = (x >> bit) & 1, yb = (y >> bit) & 1, zb = (z >> bit) & 1;
+            int nxb, nyb, nzb;
+            if (bit == 0) {
+                nxb = xb; nyb = yb; nzb = zb;
+            } else {
+                nxb = xb ? zb : xb;
+                nyb = xb ? yb : (yb ? zb : yb);
+                nzb = xb ? yb : (yb ? xb : (zb ? yb : zb));
+            }
+            result |= ((long long)nxb << (3 * bit)) | ((long long)nyb << (3 * bit + 1)) | ((long long)nzb << (3 * bit + 2));
+        }
+        key = (uint64_t)result;
+    }
+    keys[i] = key;
+    if (idx != nullptr) idx[i] = (uint32_t)i;
+}
+
+// ------------------------------------------------------------------------------------------ radix sort
+constexpr int RS_THREADS = 256;
+constexpr int RS_ITEMS = 8;
+constexpr int RS_TILE = RS_THREADS * RS_ITEMS;
+constexpr int RS_WARPS = RS_THREADS / 32;
+
+__global__ void __launch_bounds__(RS_THREADS)
+rs_hist_kernel(const uint64_t* __restrict__ keys, int64_t n, int shift, int nblocks, uint32_t* __restrict__ ghist)
+{
+    __shared__ uint32_t hist[256];
+    hist[threadIdx.x] = 0;
+    __syncthreads();
+    const int64_t base = (int64_t)blockIdx.x * RS_TILE;
+#pragma unroll
+    for (int i = 0; i < RS_ITEMS; i++) {
+        const int64_t j = base + i * RS_THREADS + threadIdx.x;
+        if (j < n) atomicAdd(&hist[(uint32_t)(keys[j] >> shift) & 255u], 1u);
+    }
+    __syncthreads();
+    ghist[(int64_t)threadIdx.x * nblocks + blockIdx.x] = hist[threadIdx.x];
+}
+
+// Stable scatter: tile order = memory order.  Round i of the tile covers elements
+// [i*256, (i+1)*256); within a round a warp covers 32 consecutive elements.  The rank of an
+// element among equal digits of the tile = (count in earlier rounds and earlier warps of its
+// round) + (count among lower lanes of its warp), the latter from __match_any_sync.
+__global__ void __launch_bounds__(RS_THREADS)
+rs_scatter_kernel(const uint64_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
+                  uint64_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n, int shift, int nblocks,
+                  const uint32_t* __restrict__ goffset)
+{
+    __shared__ uint16_t cnt[RS_ITEMS][RS_WARPS][256];
+    __shared__ uint32_t dbase[256];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int k = threadIdx.x; k < RS_ITEMS * RS_WARPS * 256; k += RS_THREADS) (&cnt[0][0][0])[k] = 0;
+    __syncthreads();
+
+    const int64_t base = (int64_t)blockIdx.x * RS_TILE;
+    uint64_t key[RS_ITEMS];
+    uint32_t val[RS_ITEMS];
+    uint16_t rank[RS_ITEMS];
+    const uint32_t lt = lanemask_lt();
+#pragma unroll
+    for (int i = 0; i < RS_ITEMS; i++) {
+        const int64_t j = base + i * RS_THREADS + threadIdx.x;
+        const bool live = j < n;
+        key[i] = live ? keys_in[j] : ~0ull;
+        val[i] = live ? vals_in[j] : 0u;
+        const uint32_t d = (uint32_t)(key[i] >> shift) & 255u;
+        // dead lanes vote with an impossible digit so that they never join a live group
+        const uint32_t peers = __match_any_sync(0xffffffffu, live ? d : 256u + lane);
+        rank[i] = (uint16_t)__popc(peers & lt);
+        if (live && (peers & lt) == 0) cnt[i][warp][d] = (uint16_t)__popc(peers);
+    }
+    __syncthreads();
+    {
+        const int d = threadIdx.x;
+        uint32_t run = 0;
+#pragma unroll
+        for (int i = 0; i < RS_ITEMS; i++)
+#pragma unroll
+            for (int w = 0; w < RS_WARPS; w++) {
+                const uint32_t c = cnt[i][w][d];
+                cnt[i][w][d] = (uint16_t)run;
+                run += c;
+            }
+        dbase[d] = goffset[(int64_t)d * nblocks + blockIdx.x];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < RS_ITEMS; i++) {
+        const int64_t j = base + i * RS_THREADS + threadIdx.x;
+        if (j < n) {
+            const uint32_t d = (uint32_t)(key[i] >> shift) & 255u;
+            const int64_t p = (int64_t)dbase[d] + cnt[i][warp][d] + rank[i];
+            keys_out[p] = key[i];
+            vals_out[p] = val[i];
+        }
+    }
+}
+
+static inline int rs_num_blocks(int64_t n) { return (int)((n + RS_TILE - 1) / RS_TILE); }
+
+struct RsLayout { int64_t keys_b, vals_b, ghist, sums, total; };
+static RsLayout rs_layout(int64_t n)
+{
+    RsLayout L;
+    int64_t o = 0;
+    auto take = [&](int64_t b) { int64_t r = o; o = align_up(o + b, 256); return r; };
+    const int nb = rs_num_blocks(n);
+    L.keys_b = take(n * 8);
+    L.vals_b = take(n * 4);
+    L.ghist = take((int64_t)nb * 256 * 4 + 64);
+    L.sums = take((int64_t)(scan_num_tiles((int64_t)nb * 256) + 1) * 8);
+    L.total = o;
+    return L;
+}
+
+// Sorts (keys, vals) by bits [begin_bit, end_bit) of the keys.  Result ends in keys/vals (the
+// caller's arrays): an odd number of passes is finished with a copy.
+static int rs_sort_pairs(uint64_t* keys, uint32_t* vals, int64_t n, int begin_bit, int end_bit, unsigned char* ws,
+                         cudaStream_t stream)
+{
+    if (n <= 0) return DYNB_OK;
+    const RsLayout L = rs_layout(n);
+    uint64_t* kb = reinterpret_cast<uint64_t*>(ws + L.keys_b);
+    uint32_t* vb = reinterpret_cast<uint32_t*>(ws + L.vals_b);
+    uint32_t* ghist = reinterpret_cast<uint32_t*>(ws + L.ghist);
+    uint32_t* sums = reinterpret_cast<uint32_t*>(ws + L.sums);
+    const int nb = rs_num_blocks(n);
+    uint64_t* kin = keys; uint32_t* vin = vals; uint64_t* kout = kb; uint32_t* vout = vb;
+    for (int shift = begin_bit; shift < end_bit; shift += 8) {
+        rs_hist_kernel<<<nb, RS_THREADS, 0, stream>>>(kin, n, shift, nb, ghist);
+        DYNB_CUDA_OK((exclusive_scan<uint32_t, uint32_t>(ghist, ghist, nullptr, (int64_t)nb * 256, sums, nullptr, stream)));
+        rs_scatter_kernel<<<nb, RS_THREADS, 0, stream>>>(kin, vin, kout, vout, n, shift, nb, ghist);
+        std::swap(kin, kout);
+        std::swap(vin, vout);
+    }
+    if (kin != keys) {
+        DYNB_CUDA_OK(cudaMemcpyAsync(keys, kin, (size_t)n * 8, cudaMemcpyDeviceToDevice, stream));
+        DYNB_CUDA_OK(cudaMemcpyAsync(vals, vin, (size_t)n * 4, cudaMemcpyDeviceToDevice, stream));
+    }
+    DYNB_CUDA_OK(cudaGetLastError());
+    return DYNB_OK;
+}
+
+// ------------------------------------------------------------------------------------------ assignment
+__global__ void __launch_bounds__(256)
+sfc_assign_unweighted_kernel(const uint32_t* __restrict__ perm, int64_t* __restrict__ labels, int64_t N, int64_t W)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const int64_t base = N / W, rem = N % W, threshold = rem * (base + 1);  // sfc_kernels.cu:123-134
+    int64_t p;
+    if (i < threshold) p = i / (base + 1);
+    else p = rem + (i - threshold) / base;
+    p = min(p, W - 1);
+    labels[perm[i]] = p;
+}
+
+__global__ void __launch_bounds__(256)
+sfc_gather_weights_kernel(const int64_t* __restrict__ w, const uint32_t* __restrict__ perm, int64_t* __restrict__ sorted_w, int64_t N)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < N) sorted_w[i] = w[perm[i]];
+}
+
+// excl[i] = sum of sorted weights before i; the reference uses the inclusive sum (:165-170)
+__global__ void __launch_bounds__(256)
+sfc_assign_weighted_kernel(const uint32_t* __restrict__ perm, const int64_t* __restrict__ sorted_w,
+                           const int64_t* __restrict__ excl, const int64_t* __restrict__ total_p,
+                           int64_t* __restrict__ labels, int64_t N, int64_t W)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const int64_t total = *total_p;
+    const int64_t cs = excl[i] + sorted_w[i];
+    int64_t p = (total > 0) ? (cs * W) / total : (int64_t)0;
+    p = max(p, (int64_t)0);
+    p = min(p, W - 1);
+    labels[perm[i]] = p;
+}
+
+__global__ void __launch_bounds__(256) fill_i64_kernel(int64_t* p, int64_t n, int64_t v)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = v;
+}
+
+__global__ void __launch_bounds__(256) u32_to_i64_kernel(const uint32_t* a, int64_t* b, int64_t n)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) b[i] = (int64_t)a[i];
+}
+
+struct SfcLayout { int64_t bounds, keys, idx, sorted_w, excl, total_w, sums, rs, total; };
+static SfcLayout sfc_layout(int64_t n)
+{
+    SfcLayout L;
+    int64_t o = 0;
+    auto take = [&](int64_t b) { int64_t r = o; o = align_up(o + b, 256); return r; };
+    L.bounds = take(sizeof(SfcBounds));
+    L.keys = take(n * 8);
+    L.idx = take(n * 4);
+    L.sorted_w = take(n * 8);
+    L.excl = take(n * 8);
+    L.total_w = take(64);
+    L.sums = take((int64_t)(scan_num_tiles(n) + 1) * 8);
+    L.rs = take(rs_layout(n).total);
+    L.total = o;
+    return L;
+}
+
+static int sfc_keys_into(const float* pos, int64_t n, int curve, unsigned char* ws, const SfcLayout& L, uint64_t* keys,
+                         uint32_t* idx, cudaStream_t stream)
+{
+    SfcBounds init;
+    for (int k = 0; k < 3; k++) { init.mn[k] = 0xffffffffu; init.mx[k] = 0u; init.pmin[k] = 0.f; init.prange[k] = 1.f; }
+    SfcBounds* b = reinterpret_cast<SfcBounds*>(ws + L.bounds);
+    DYNB_CUDA_OK(cudaMemcpyAsync(b, &init, sizeof(init), cudaMemcpyHostToDevice, stream));
+    const int grid = (int)std::min<int64_t>((n + 255) / 256, (int64_t)sm_count_cached() * 8);
+    sfc_minmax_kernel<<<grid, 256, 0, stream>>>(pos, n, b);
+    sfc_bounds_finish_kernel<<<1, 32, 0, stream>>>(b);
+    const unsigned nbk = (unsigned)((n + 255) / 256);
+    if (curve == 0) sfc_keys_kernel<0><<<nbk, 256, 0, stream>>>(pos, n, b, keys, idx);
+    else sfc_keys_kernel<1><<<nbk, 256, 0, stream>>>(pos, n, b, keys, idx);
+    DYNB_CUDA_OK(cudaGetLastError());
+    return DYNB_OK;
+}
+
+}  // namespace dynb
+
+using namespace dynb;
+
+extern "C" int dynb_sfc_workspace_bytes(int64_t n_atoms, int64_t* bytes)
+{
+    if (n_atoms < 0 || bytes == nullptr || n_atoms >= (1ll << 32) - 1) return fail_arg("bad arguments");
+    *bytes = sfc_layout(std::max<int64_t>(n_atoms, 1)).total;
+    return DYNB_OK;
+}
+
+extern "C" int dynb_sfc_keys(const float* pos_dev, int64_t n_atoms, int curve_type, int64_t* keys_dev, void* workspace_dev,
+                             int64_t workspace_bytes, void* stream)
+{
+    if (n_atoms < 0 || (curve_type != 0 && curve_type != 1)) return fail_arg("curve_type must be 0 (Morton) or 1 (Hilbert)");
+    if (n_atoms == 0) return DYNB_OK;
+    if (pos_dev == nullptr || keys_dev == nullptr || workspace_dev == nullptr) return fail_arg("null pointer");
+    const SfcLayout L = sfc_layout(n_atoms);
+    if (workspace_bytes < L.total) return fail_arg("workspace too small (see dynb_sfc_workspace_bytes)");
+    return sfc_keys_into(pos_dev, n_atoms, curve_type, static_cast<unsigned char*>(workspace_dev), L,
+                         reinterpret_cast<uint64_t*>(keys_dev), nullptr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dynb_sfc_partition(const float* pos_dev, int64_t n_atoms, const int64_t* weights_dev, int64_t W, int curve_type,
+                                  int64_t* labels_dev, int64_t* perm_dev, void* workspace_dev, int64_t workspace_bytes,
+                                  void* stream)
+{
+    if (n_atoms < 0) return fail_arg("n_atoms must be non-negative");
+    if (W < 1) return fail_arg("W must be >= 1");
+    if (curve_type != 0 && curve_type != 1) return fail_arg("curve_type must be 0 (Morton) or 1 (Hilbert)");
+    if (n_atoms == 0) return DYNB_OK;
+    if (pos_dev == nullptr || labels_dev == nullptr || workspace_dev == nullptr) return fail_arg("null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const unsigned nbk = (unsigned)((n_atoms + 255) / 256);
+    if (W == 1 && perm_dev == nullptr) {  // sfc_kernels.cu:192-194
+        fill_i64_kernel<<<nbk, 256, 0, s>>>(labels_dev, n_atoms, 0);
+        DYNB_CUDA_OK(cudaGetLastError());
+        return DYNB_OK;
+    }
+    const SfcLayout L = sfc_layout(n_atoms);
+    if (workspace_bytes < L.total) return fail_arg("workspace too small (see dynb_sfc_workspace_bytes)");
+    unsigned char* ws = static_cast<unsigned char*>(workspace_dev);
+    uint64_t* keys = reinterpret_cast<uint64_t*>(ws + L.keys);
+    uint32_t* idx = reinterpret_cast<uint32_t*>(ws + L.idx);
+    int rc = sfc_keys_into(pos_dev, n_atoms, curve_type, ws, L, keys, idx, s);
+    if (rc) return rc;
+    rc = rs_sort_pairs(keys, idx, n_atoms, 0, curve_type == 0 ? 64 : 24, ws + L.rs, s);
+    if (rc) return rc;
+    if (W == 1) {
+        fill_i64_kernel<<<nbk, 256, 0, s>>>(labels_dev, n_atoms, 0);
+    } else if (weights_dev != nullptr) {
+        int64_t* sorted_w = reinterpret_cast<int64_t*>(ws + L.sorted_w);
+        int64_t* excl = reinterpret_cast<int64_t*>(ws + L.excl);
+        int64_t* total = reinterpret_cast<int64_t*>(ws + L.total_w);
+        sfc_gather_weights_kernel<<<nbk, 256, 0, s>>>(weights_dev, idx, sorted_w, n_atoms);
+        DYNB_CUDA_OK((exclusive_scan<long long, long long>(reinterpret_cast<long long*>(sorted_w), reinterpret_cast<long long*>(excl),
+                                                            nullptr, n_atoms, reinterpret_cast<long long*>(ws + L.sums),
+                                                            reinterpret_cast<long long*>(total), s)));
+        sfc_assign_weighted_kernel<<<nbk, 256, 0, s>>>(idx, sorted_w, excl, total, labels_dev, n_atoms, W);
+    } else {
+        sfc_assign_unweighted_kernel<<<nbk, 256, 0, s>>>(idx, labels_dev, n_atoms, W);
+    }
+    if (perm_dev != nullptr) u32_to_i64_kernel<<<nbk, 256, 0, s>>>(idx, perm_dev, n_atoms);
+    DYNB_CUDA_OK(cudaGetLastError());
+    return DYNB_OK;
+}
+
+extern "C" int dynb_radix_sort_workspace_bytes(int64_t n, int64_t* bytes)
+{
+    if (n < 0 || bytes == nullptr) return fail_arg("bad arguments");
+    *bytes = rs_layout(std::max<int64_t>(n, 1)).total;
+    return DYNB_OK;
+}
+
+extern "C" int dynb_radix_sort_pairs(uint64_t* keys_dev, uint32_t* vals_dev, int64_t n, int begin_bit, int end_bit,
+                                     void* workspace_dev, int64_t workspace_bytes, void* stream)
+{
+    if (n < 0 || begin_bit < 0 || end_bit > 64 || begin_bit >= end_bit || (begin_bit % 8) != 0)
+        return fail_arg("bad bit range (begin_bit must be a multiple of 8, end_bit <= 64)");
+    if (n == 0) return DYNB_OK;
+    if (keys_dev == nullptr || vals_dev == nullptr || workspace_dev == nullptr) return fail_arg("null pointer");
+    if (workspace_bytes < rs_layout(n).total) return fail_arg("workspace too small");
+    return rs_sort_pairs(keys_dev, vals_dev, n, begin_bit, end_bit, static_cast<unsigned char*>(workspace_dev),
+                         static_cast<cudaStream_t>(stream));
+}

@@ -86,6 +86,83 @@ int dynb_rg_plan(const void* pos_dev, int dtype, int64_t n_atoms, const void* ce
 int dynb_rg_fill(const void* workspace_dev, int dtype, int64_t* edge_index_dev /* [2,E] */,
                  float* cell_shifts_dev /* [E,3] */, void* dist_sq_dev /* [E] or NULL */, int64_t E, void* stream);
 
+/* Halo marking over a plan (all atoms as targets, radius = cutoff + ghost buffer): for every edge
+ * src -> dst whose endpoints have different owners, sets bit owner[dst] of
+ * needed_dev[src * words + ...] (words = ceil(world_size / 32)) and has_foreign_dev[dst] = 1.
+ * Both outputs are cleared first.  This is the edge loop of build_halo_maps
+ * (dynamis_state/src/csrc/build_halo_maps.cpp:50-58, 127-138) without materialising the graph. */
+int dynb_rg_halo_mark(const void* workspace_dev, int dtype, const int64_t* owner_dev, int64_t n_atoms,
+                      int64_t world_size, uint32_t* needed_dev, uint8_t* has_foreign_dev, void* stream);
+
+/* ------------------------------------------------------------------ SFC partition
+ * Replaces sfc_partition_cuda (dynamis_state/src/csrc/partition/sfc.cpp:9-33,
+ * sfc_kernels.cu:178-251): labels_dev[i] in [0, W) for every atom.  curve_type 0 = Morton
+ * (21 bits per axis), 1 = the reference's 7-bit "Hilbert" transform.  weights_dev: int64 per-atom
+ * cost or NULL (equal counts).  perm_dev (optional): atom indices in curve order.
+ * Atoms with equal keys are ordered by ascending index (the reference leaves ties unspecified). */
+int dynb_sfc_workspace_bytes(int64_t n_atoms, int64_t* bytes);
+int dynb_sfc_partition(const float* pos_dev, int64_t n_atoms, const int64_t* weights_dev, int64_t W, int curve_type,
+                       int64_t* labels_dev, int64_t* perm_dev, void* workspace_dev, int64_t workspace_bytes,
+                       void* stream);
+/* Keys alone, in atom order (sfc_kernels.cu:32-109). */
+int dynb_sfc_keys(const float* pos_dev, int64_t n_atoms, int curve_type, int64_t* keys_dev, void* workspace_dev,
+                  int64_t workspace_bytes, void* stream);
+/* Stable LSD radix sort of (uint64 key, uint32 value) pairs on key bits [begin_bit, end_bit), in
+ * place (replaces the at::sort call at sfc_kernels.cu:224). */
+int dynb_radix_sort_workspace_bytes(int64_t n, int64_t* bytes);
+int dynb_radix_sort_pairs(uint64_t* keys_dev, uint32_t* vals_dev, int64_t n, int begin_bit, int end_bit,
+                          void* workspace_dev, int64_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------ partition bookkeeping
+ * atom_counts = bincount(labels) and partition_indices = vertex_numbers[nonzero(labels == R)]
+ * (dynamis_state/src/csrc/partition/sfc_partitioner.cpp:166-176).  bad_dev: one uint32, non-zero
+ * when a value fell outside [0, W).  dynb_select_eq_i64 writes at most n values to out_dev
+ * (ascending positions; gather_src_dev[i] instead of i when given) and the count to count_dev. */
+int dynb_bincount_i64(const int64_t* a_dev, int64_t n, int64_t W, int64_t* counts_dev, uint32_t* bad_dev, void* stream);
+int dynb_select_workspace_bytes(int64_t n, int64_t* bytes);
+int dynb_select_eq_i64(const int64_t* a_dev, int64_t n, int64_t value, const int64_t* gather_src_dev,
+                       int64_t* out_dev, int64_t* count_dev, void* workspace_dev, int64_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------ halo maps
+ * Per-edge pass of extract_halo_info (dynamis_state/src/csrc/graph/dist_graph_ops_kernels.cu:46-59,
+ * 104-188): edges_dev [2,E] with dst owned by my_rank.  Clears and fills
+ * recv_mask_dev[src] |= bit pid[src], send_mask_dev[dst] |= bit pid[src], has_remote_dev[dst] = 1 for
+ * every edge whose source belongs to another rank (masks are [N, ceil(W/32)] uint32). */
+int dynb_halo_mark_from_edges(const int64_t* edges_dev, int64_t E, const int64_t* pid_dev, int64_t N, int64_t my_rank,
+                              int64_t world_size, uint32_t* send_mask_dev, uint32_t* recv_mask_dev,
+                              uint8_t* has_remote_dev, uint32_t* bad_dev, void* stream);
+
+/* CSR assembly (build_halo_maps.cpp:60-125; dist_graph_ops_kernels.cu:143-177).  Element a in
+ * [0, n) carries a set of peer ranks; segment p of the output lists, ascending in a, the elements
+ * whose set contains p.  mode 0 (send): owner[a] == R ? mask bits without R : {};
+ * mode 1 (recv): owner[a] != R and bit R of mask[a] ? {owner[a]} : {};  mode 2: the mask bits.
+ * dynb_csr_plan writes offsets_dev [W+1]; after reading offsets[W] the caller allocates out_dev and
+ * calls dynb_csr_fill with the same arguments and workspace (value_map_dev[a] is written instead
+ * of a when given). */
+int dynb_csr_workspace_bytes(int64_t n, int64_t W, int64_t* bytes);
+int dynb_csr_plan(const uint32_t* mask_dev, const int64_t* owner_dev, int64_t n, int64_t R, int mode, int64_t W,
+                  int64_t* offsets_dev, void* workspace_dev, int64_t workspace_bytes, void* stream);
+int dynb_csr_fill(const uint32_t* mask_dev, const int64_t* owner_dev, int64_t n, int64_t R, int mode, int64_t W,
+                  const int64_t* value_map_dev, const int64_t* offsets_dev, int64_t* out_dev,
+                  const void* workspace_dev, void* stream);
+/* interior_mask[i] = !flags[idx[i]] (build_halo_maps.cpp:138). */
+int dynb_gather_not_u8(const uint8_t* flags_dev, const int64_t* idx_dev, int64_t n, uint8_t* out_dev, void* stream);
+/* g2l[idx[i]] = i (dist_graph_ops_kernels.cu:143-144). */
+int dynb_scatter_iota(const int64_t* idx_dev, int64_t n, int64_t N, int64_t* g2l_dev, uint32_t* bad_dev, void* stream);
+
+/* ------------------------------------------------------------------ edge filter
+ * filter_edges_to_radius (dynamis_state/src/csrc/graph/dist_graph_ops.cpp:5-37,
+ * dist_graph_ops_kernels.cu:16-43, 62-102): keeps edge e iff
+ * |pos[src] + shift @ cell - pos[dst]|^2 <= radius^2 (float32), order preserving.  The plan writes
+ * the number kept to count_dev; the fill compacts edges [2,E] -> [2,E_out] and the shift rows of
+ * any element size (shift_row_bytes = 3 * element size).  Workspace: dynb_select_workspace_bytes(2*E). */
+int dynb_filter_edges_plan(const int64_t* edges_dev, const float* shifts_f32_dev, const float* pos_dev,
+                           const float* cell_host, double radius, int64_t E, int64_t* count_dev,
+                           void* workspace_dev, int64_t workspace_bytes, void* stream);
+int dynb_filter_edges_fill(const int64_t* edges_dev, const void* shifts_raw_dev, int shift_row_bytes, int64_t E,
+                           int64_t E_out, int64_t* edges_out_dev, void* shifts_out_dev, const void* workspace_dev,
+                           void* stream);
+
 #ifdef __cplusplus
 }
 #endif
