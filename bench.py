@@ -183,7 +183,7 @@ def run_ours(args):
 
         dist.init_process_group("nccl", device_id=dev)
     if world > 1:
-        from dynamis_b200 import bench_multi
+        import bench_multi
 
         return bench_multi.run(args, rank, world, dev)
 

@@ -14,6 +14,15 @@ from .graph import (  # noqa: F401
     radius_graph_pbc_ex,
     radius_graph_pbc_with_dist,
 )
+from .exchange import (  # noqa: F401
+    Exchanger,
+    FeatureExchanger,
+    FeaturePushToExchange,
+    GPUDirectExchanger,
+    PythonNCCLExchanger,
+    drift_flags,
+    push_buffer_create,
+)
 from .halo import extract_halo_info, filter_edges_to_radius  # noqa: F401
 from .partition import (  # noqa: F401
     SFCCurveType,

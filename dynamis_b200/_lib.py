@@ -64,6 +64,20 @@ SIGNATURES = {
     "dynb_scatter_iota": (_i32, [_p, _i64, _i64, _p, _p, _p]),
     "dynb_filter_edges_plan": (_i32, [_p, _p, _p, _p, _f64, _i64, _p, _p, _i64, _p]),
     "dynb_filter_edges_fill": (_i32, [_p, _p, _i32, _i64, _i64, _p, _p, _p, _p]),
+    "dynb_pack_rows": (_i32, [_p, _i64, _i64, _p, _i64, _p, _p, _p]),
+    "dynb_push_rows": (_i32, [_p, _i64, _p, _i64, _p, _i32, _i64, _i32, _p]),
+    "dynb_signal_peers": (_i32, [_p, _i32, ctypes.c_uint32, _p]),
+    "dynb_wait_flags": (_i32, [_p, _p, _i32, ctypes.c_uint32, _i64, _p, _p]),
+    "dynb_inverse_csr_workspace_bytes": (_i32, [_i64, _i64, ctypes.POINTER(_i64)]),
+    "dynb_inverse_csr": (_i32, [_p, _i64, _i64, _p, _p, _p, _p, _i64, _p]),
+    "dynb_unpack_add_rows": (_i32, [_p, _i64, _i64, _i32, _p, _p, _p, _p, _p]),
+    "dynb_ipc_alloc": (_i32, [_i64, ctypes.POINTER(_p)]),
+    "dynb_ipc_free": (_i32, [_p]),
+    "dynb_ipc_export": (_i32, [_p, _p]),
+    "dynb_ipc_open": (_i32, [_p, ctypes.POINTER(_p)]),
+    "dynb_ipc_close": (_i32, [_p]),
+    "dynb_enable_peer_access": (_i32, [_i32]),
+    "dynb_copy_async": (_i32, [_p, _p, _i64, _p]),
 }
 
 _LIB = None

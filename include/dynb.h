@@ -163,6 +163,64 @@ int dynb_filter_edges_fill(const int64_t* edges_dev, const void* shifts_raw_dev,
                            int64_t E_out, int64_t* edges_out_dev, void* shifts_out_dev, const void* workspace_dev,
                            void* stream);
 
+/* ------------------------------------------------------------------ halo exchange
+ * Row gather  out[i, :] = input[locs[i], :]  (push_buffer_create,
+ * dynamis_model/src/csrc/push_buffer.cu:39-105); rows are row_bytes bytes of any dtype.
+ * bad_dev (optional uint32): set non-zero when a loc falls outside [0, n_rows_in); that row is skipped. */
+int dynb_pack_rows(const void* input_dev, int64_t n_rows_in, int64_t row_bytes, const int64_t* locs_dev, int64_t n,
+                   void* out_dev, uint32_t* bad_dev, void* stream);
+
+/* One peer segment of a push: rows [start, start + count) of the logical send list are stored
+ * into remote_ptr (a peer's mapped buffer) starting at row remote_row_offset.  Same role as the
+ * reference's PushTarget (dynamis_model/include/dynamis_model/exchanger.hpp:13-18). */
+typedef struct dynb_push_target {
+    void* remote_ptr;
+    int64_t remote_row_offset;
+    int64_t start;
+    int64_t count;
+} dynb_push_target;
+
+/* Fused gather + store into peers' memory over NVLink (gather_and_push_kernel and
+ * gather_ghost_grad_and_push_kernel, dynamis_model/src/csrc/exchange/ipc_exchange_kernels.cu:40-122).
+ * row_index_dev != NULL: logical row i is x[row_index_dev[i]] (forward push of send_local_indices);
+ * NULL: logical row i is x[src_row_base + i] (backward push of the contiguous ghost rows).
+ * remote_align: guaranteed byte alignment of every remote row start (16 when the remote buffers
+ * and row_bytes are 16-byte multiples). */
+int dynb_push_rows(const void* x_dev, int64_t row_bytes, const int64_t* row_index_dev, int64_t src_row_base,
+                   const dynb_push_target* targets_dev, int n_targets, int64_t total_rows, int remote_align, void* stream);
+
+/* Generation signalling (record_push_complete / wait_for_pushes,
+ * dynamis_model/src/csrc/exchange/ipc_exchanger.cpp:784-828).  dynb_signal_peers release-stores
+ * `value` into each non-NULL remote flag; dynb_wait_flags waits until flags_dev[k] >= value for every k
+ * with expect_dev[k] != 0 (all k when expect_dev is NULL), for at most timeout_ns; on expiry
+ * *status_dev becomes 1 + k of a flag that never arrived (0 = all arrived) and the kernel returns. */
+int dynb_signal_peers(uint32_t* const* remote_flag_ptrs_dev, int n, uint32_t value, void* stream);
+int dynb_wait_flags(const uint32_t* flags_dev, const uint8_t* expect_dev, int n, uint32_t value, int64_t timeout_ns,
+                    uint32_t* status_dev, void* stream);
+
+/* Reverse halo: out[i, :] = grad[i, :] + sum of the received rows that name local row i, in fixed
+ * peer order (replaces clone + index_add_, dynamis_model/src/csrc/exchanger.cu:111-117, which
+ * accumulates with float atomics).  dynb_inverse_csr builds, once per halo plan, for every local
+ * row the positions of the send list that name it. */
+int dynb_inverse_csr_workspace_bytes(int64_t total_send, int64_t n_local, int64_t* bytes);
+int dynb_inverse_csr(const int64_t* send_local_dev, int64_t total_send, int64_t n_local, int64_t* inv_offsets_dev,
+                     uint32_t* inv_entries_dev, uint32_t* bad_dev, void* workspace_dev, int64_t workspace_bytes,
+                     void* stream);
+int dynb_unpack_add_rows(const void* grad_dev, int64_t n_local, int64_t feature_dim, int dtype, const void* recv_dev,
+                         const int64_t* inv_offsets_dev, const uint32_t* inv_entries_dev, void* out_dev, void* stream);
+
+/* Peer-visible memory (allocate_ipc_buffer / export_ipc_handle / cudaIpcOpenMemHandle,
+ * dynamis_model/src/csrc/exchange/ipc_exchanger.cpp:117-252, 406-430).  These are the only calls of
+ * the library that allocate, free or map device memory; dynb_ipc_alloc zero-fills and synchronises. */
+int dynb_ipc_alloc(int64_t bytes, void** ptr_out);
+int dynb_ipc_free(void* ptr);
+int dynb_ipc_export(void* ptr, uint8_t* handle64_out);
+int dynb_ipc_open(const uint8_t* handle64, void** ptr_out);
+int dynb_ipc_close(void* ptr);
+int dynb_enable_peer_access(int peer_device);
+/* Device-to-device copy on the stream (the local rows and ghost rows of the concatenated result). */
+int dynb_copy_async(void* dst_dev, const void* src_dev, int64_t bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
