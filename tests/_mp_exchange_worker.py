@@ -1,0 +1,78 @@
+"""Worker for test_multi_gpu.py: one rank per GPU under torchrun.  Builds a halo plan for a small
+system (CPU oracle), runs both exchangers forward and backward on real GPUs and checks the results
+against the oracle.  Exits non-zero on any mismatch."""
+
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import dynamis_b200 as D  # noqa: E402
+from oracle import cpu_oracle as O  # noqa: E402
+
+
+def main():
+    rank, W = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    rng = np.random.default_rng(99)
+    n, L = 20000, 64.0
+    pos = (rng.random((n, 3)) * L).astype(np.float32)
+    cell = (np.eye(3) * L).astype(np.float32)
+
+    # partition + halo maps through the product path on this rank's GPU
+    st = D.MolecularInfo()
+    st.num_atoms, st.atom_positions = n, torch.as_tensor(pos, device=dev)
+    st.atom_vertex_numbers = torch.arange(n, dtype=torch.int64, device=dev)
+    env = D.DistEnvironment()
+    env.global_rank, env.world_size = rank, W
+    cfg = D.SimulationConfig()
+    cfg.cutoff, cfg.ghost_cutoff_buffer, cfg.cell, cfg.pbc = 6.0, 0.5, torch.as_tensor(cell), torch.tensor([True] * 3)
+    part = D.SFCPartitioner()
+    info = part.partition(st, env)
+    part.build_halo_maps(info, st, env, cfg)
+
+    # the oracle's view of every rank
+    g = O.radius_graph(pos, cell, [1, 1, 1], np.float32(6.5))
+    pid = O.sfc_partition(pos, None, W, 0)
+    maps = [O.build_halo_maps(g["src"], g["dst"], pid, r, W) for r in range(W)]
+    assert np.array_equal(info.send_local_indices.cpu().numpy(), maps[rank]["send_local_indices"])
+    assert np.array_equal(info.recv_offsets.cpu().numpy(), maps[rank]["recv_offsets"])
+    so = [m["send_offsets"] for m in maps]
+    sl = [m["send_local_indices"] for m in maps]
+    ro = [m["recv_offsets"] for m in maps]
+    nl = [m["num_local"] for m in maps]
+    state = D.DynamisState()
+    state.local_partition_info = info
+
+    for make in (lambda: D.GPUDirectExchanger(wait_ns=10_000_000_000), lambda: D.PythonNCCLExchanger()):
+        for F in (3, 128):
+            ex = make()
+            frng = np.random.default_rng(1234 + F)
+            feats = [frng.standard_normal((nl[r], F)).astype(np.float32) for r in range(W)]
+            ref = O.exchange_forward(feats, so, sl, ro)
+            grads = [frng.standard_normal(ref[r].shape).astype(np.float32) for r in range(W)]
+            refb = O.exchange_backward(grads, nl, so, sl, ro)
+            for it in range(3):
+                x = torch.as_tensor(feats[rank], device=dev).requires_grad_(True)
+                out = D.FeaturePushToExchange.apply(x, state, ex)
+                assert np.array_equal(out.detach().cpu().numpy(), ref[rank]), f"forward mismatch {type(ex).__name__} F={F}"
+                out.backward(torch.as_tensor(grads[rank], device=dev))
+                np.testing.assert_allclose(x.grad.cpu().numpy(), refb[rank], rtol=1e-6, atol=1e-6)
+            if hasattr(ex, "exchanger"):
+                ex.exchanger.check_status()
+            dist.barrier()
+            ex.reset_buffers()
+    dist.barrier()
+    dist.destroy_process_group()
+    print(f"rank {rank}: ok", flush=True)
+
+
+if __name__ == "__main__":
+    main()
