@@ -410,3 +410,42 @@ extern "C" int dynb_radix_sort_pairs(uint64_t* keys_dev, uint32_t* vals_dev, int
     return rs_sort_pairs(keys_dev, vals_dev, n, begin_bit, end_bit, static_cast<unsigned char*>(workspace_dev),
                          static_cast<cudaStream_t>(stream));
 }
+
+// ------------------------------------------------------------------------------------------ no-allocation variant
+// Some hosts of this library may not allocate device memory at all while they run: an MD engine that
+// hands its whole memory budget to its own pool at start-up, a plugin living inside another runtime's
+// allocator, a latency-critical loop where a cudaMalloc (which synchronises the device) is not
+// acceptable.  They cannot provide the workspace dynb_sfc_partition asks for.  This variant keeps that
+// workspace in a fixed device array that is part of the library image, so every GPU that loads the
+// library carries DYNB_SFC_STATIC_BYTES of it until the process exits, and problems larger than
+// DYNB_SFC_STATIC_MAX_ATOMS are refused.
+constexpr int64_t DYNB_SFC_STATIC_MAX_ATOMS_C = 131072;
+constexpr int64_t DYNB_SFC_STATIC_BYTES = 6ll << 20;
+static __device__ __align__(256) unsigned char g_sfc_static_scratch[DYNB_SFC_STATIC_BYTES];
+// Device address of the array, per device.  In host code the array's name is only a stand-in and
+// must never be handed to a kernel; cudaGetSymbolAddress gives the real address for the current device.
+static void* g_sfc_static_addr[64] = {nullptr};
+
+extern "C" int64_t dynb_sfc_static_max_atoms(void) { return DYNB_SFC_STATIC_MAX_ATOMS_C; }
+
+extern "C" int dynb_sfc_partition_static(const float* pos_dev, int64_t n_atoms, const int64_t* weights_dev, int64_t W,
+                                         int curve_type, int64_t* labels_dev, int64_t* perm_dev, void* stream)
+{
+    if (n_atoms < 0) return dynb::fail_arg("n_atoms must be non-negative");
+    if (n_atoms > DYNB_SFC_STATIC_MAX_ATOMS_C)
+        return dynb::fail_arg("dynb_sfc_partition_static: n_atoms exceeds the built-in scratch (limit 131072 atoms); "
+                              "use dynb_sfc_partition with a caller-provided workspace");
+    if (dynb::sfc_layout(std::max<int64_t>(n_atoms, 1)).total > DYNB_SFC_STATIC_BYTES)
+        return dynb::fail_arg("dynb_sfc_partition_static: built-in scratch too small for this size");
+    int dev = 0;
+    DYNB_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return dynb::fail_arg("device ordinal out of range");
+    if (g_sfc_static_addr[dev] == nullptr) {
+        void* p = nullptr;
+        DYNB_CUDA_OK(cudaGetSymbolAddress(&p, g_sfc_static_scratch));
+        if (p == nullptr) return dynb::fail_arg("cudaGetSymbolAddress returned a null address");
+        g_sfc_static_addr[dev] = p;
+    }
+    return dynb_sfc_partition(pos_dev, n_atoms, weights_dev, W, curve_type, labels_dev, perm_dev, g_sfc_static_addr[dev],
+                              DYNB_SFC_STATIC_BYTES, stream);
+}

@@ -221,6 +221,25 @@ int dynb_enable_peer_access(int peer_device);
 /* Device-to-device copy on the stream (the local rows and ghost rows of the concatenated result). */
 int dynb_copy_async(void* dst_dev, const void* src_dev, int64_t bytes, void* stream);
 
+/* ------------------------------------------------------------------ partition without a workspace
+ * No counterpart in the reference.  Same result as dynb_sfc_partition, for callers that must not
+ * allocate device memory while they run (an engine that gave its whole memory budget to its own
+ * pool, a plugin inside another runtime's allocator, a loop that cannot afford the device-wide
+ * synchronisation of cudaMalloc): the sort and scan scratch lives in a fixed array inside the
+ * library image (6 MiB per GPU that loads the library, held until the process exits) instead of a
+ * caller-provided workspace.  Limits and rules:
+ *   - n_atoms <= dynb_sfc_static_max_atoms() (131072); larger inputs are rejected with DYNB_ERR_ARG.
+ *   - The call itself allocates and frees nothing (no cudaMalloc / cudaFree, no allocating library
+ *     routine); inputs and outputs are the caller's.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current).  Make that first call before starting any stream capture.
+ *   - All calls on a device share the one array, which still holds the previous call's contents;
+ *     nothing in it needs to start at zero (every region is rewritten before it is read).  Two calls
+ *     that overlap on the GPU (different streams, or two host threads) race on it: serialise them. */
+int64_t dynb_sfc_static_max_atoms(void);
+int dynb_sfc_partition_static(const float* pos_dev, int64_t n_atoms, const int64_t* weights_dev, int64_t W,
+                              int curve_type, int64_t* labels_dev, int64_t* perm_dev, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
