@@ -69,6 +69,27 @@ def main():
                 ex.exchanger.check_status()
             dist.barrier()
             ex.reset_buffers()
+    # DistGraphBuilder across real ranks: the union of the ranks' edges is the full graph, the halo
+    # CSR equals the oracle's build_halo_maps for the partition the ranks agreed on
+    from dynamis_b200.dist_graph_builder import BuildMode, DistGraphBuilder
+
+    b = DistGraphBuilder(torch.as_tensor(cell, device=dev), torch.tensor([True] * 3), 6.0, 0.5, env, refresh_interval=5)
+    tp = torch.as_tensor(pos, device=dev)
+    gfull = O.radius_graph(pos, cell, [1, 1, 1], 6.0)
+    for it in range(2):
+        res = b.build(tp)
+        assert res.mode == (BuildMode.REFRESH if it == 0 else BuildMode.STEADY)
+        assert np.array_equal(res.full_degrees.cpu().numpy(), gfull["counts"])
+        pid_b = res.pid_outer.cpu().numpy()
+        assert np.array_equal(pid_b, O.sfc_partition(pos, gfull["counts"].astype(np.int64), W, 0))
+        mb = O.build_halo_maps(g["src"], g["dst"], pid_b, rank, W)
+        assert np.array_equal(res.halo_info.send_local_indices.cpu().numpy(), mb["send_local_indices"])
+        assert np.array_equal(res.halo_recv_global_ids.cpu().numpy(), mb["recv_atom_global"])
+        assert np.array_equal(res.interior_mask.cpu().numpy(), mb["interior_mask"])
+        mine = O.canonical_edges(res.edges_outer[0].cpu().numpy(), res.edges_outer[1].cpu().numpy(), res.cell_shifts_outer.cpu().numpy())
+        sel = pid_b[gfull["dst"]] == rank
+        want = O.canonical_edges(gfull["src"][sel], gfull["dst"][sel], gfull["shift"][sel])
+        assert mine.shape == want.shape and (mine == want).all(), f"DistGraphBuilder edges differ (pass {it})"
     dist.barrier()
     dist.destroy_process_group()
     print(f"rank {rank}: ok", flush=True)
