@@ -31,6 +31,8 @@
 #include "scan.cuh"
 
 #include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 namespace dynb {
@@ -51,7 +53,7 @@ struct DevHeader {
     uint32_t ncell_plus1;
     int32_t pad;
     int32_t gx;
-    int32_t unused;
+    int32_t group_cells_y;  // cells per warp work item along y (1 or 2)
     unsigned long long bb_min[3];  // ordered-integer images of the bounding box
     unsigned long long bb_max[3];
     double gmin[3];
@@ -193,7 +195,15 @@ rg_wrap_kernel(const T* __restrict__ pos, int64_t N, Geom<T> g, int vec_ok, Vec4
                 if (!(s[d] <= (T)1.0f - g.cf[d])) flags |= (8u << d);       // :58
             }
         }
-        if (!(status & DYNB_RG_NONFINITE)) {
+        if (!(status & DYNB_RG_NONFINITE) && flags == 0) {
+            // interior atom: only its own (0,0,0) image
+            T x, y, z;
+            image_pos(g, wx, wy, wz, 0, 0, 0, x, y, z);
+            mn[0] = mx[0] = ordered_any(x);
+            mn[1] = mx[1] = ordered_any(y);
+            mn[2] = mx[2] = ordered_any(z);
+            count = 1;
+        } else if (!(status & DYNB_RG_NONFINITE)) {
             for (int dx = -g.rep[0]; dx <= g.rep[0]; dx++)
                 for (int dy = -g.rep[1]; dy <= g.rep[1]; dy++)
                     for (int dz = -g.rep[2]; dz <= g.rep[2]; dz++) {
@@ -251,7 +261,8 @@ rg_wrap_kernel(const T* __restrict__ pos, int64_t N, Geom<T> g, int vec_ok, Vec4
 // grow, and once they are wider than the cutoff the scan shrinks to +-1.
 // ------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void rg_grid_kernel(DevHeader* h, double radius, long long src_capacity, long long cell_capacity)
+__global__ void rg_grid_kernel(DevHeader* h, double radius, long long src_capacity, long long cell_capacity, int cand_capacity,
+               int force_sx, int force_sy)
 {
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     if (h->M > (unsigned long long)src_capacity) h->status |= DYNB_RG_SRC_OVERFLOW;
@@ -260,6 +271,7 @@ __global__ void rg_grid_kernel(DevHeader* h, double radius, long long src_capaci
         h->ncell_plus1 = 2;
         h->pad = 1;
         h->group_cells = 1;
+        h->group_cells_y = 1;
         h->gx = 1;
         h->num_groups = 0;
         h->gmin[0] = h->gmin[1] = h->gmin[2] = 0.0;
@@ -293,15 +305,31 @@ __global__ void rg_grid_kernel(DevHeader* h, double radius, long long src_capaci
     h->pad = pad;
     for (int k = 0; k < 3; k++) h->gmin[k] = lo[k];
     h->res_inv = 1.0 / res;
-    // cells per warp work item: keep the expected dense candidate list near 300 records
+    // cells per warp work item (Sx along x, Sy along y): as many target cells as possible while the
+    // expected dense candidate list stays within 1.5 shared-memory lists
     const double avg = (double)h->M / (double)ncell;
-    const double rows = (double)((2 * pad + 1) * (2 * pad + 1));
-    int S = (int)floor(300.0 / (rows * (avg > 1e-6 ? avg : 1e-6))) - 2 * pad;
-    S = S < 1 ? 1 : (S > 4 ? 4 : S);
-    if (S > h->nx) S = h->nx;
-    h->group_cells = S;
-    h->gx = (h->nx + S - 1) / S;
-    h->num_groups = (unsigned long long)h->gx * (unsigned long long)h->ny * (unsigned long long)h->nz;
+    const double budget = 1.5 * (double)cand_capacity;  // a second chunk costs less than smaller groups (measured)
+    int bestx = 1, besty = 1;
+    double best_per_target = 1e300;
+    for (int sy = 1; sy <= 2; sy++)
+        for (int sx = 1; sx <= 4; sx++) {
+            if ((sy + 2 * pad) * (2 * pad + 1) > 32) continue;  // one lane per candidate run
+            const double Lexp = (double)(sx + 2 * pad) * (double)(sy + 2 * pad) * (double)(2 * pad + 1) * (avg > 1e-6 ? avg : 1e-6);
+            if (Lexp > budget && !(sx == 1 && sy == 1)) continue;
+            const int cells = sx * sy;
+            if (cells > bestx * besty || (cells == bestx * besty && Lexp / cells < best_per_target)) {
+                bestx = sx; besty = sy; best_per_target = Lexp / cells;
+            }
+        }
+    if (force_sx > 0) bestx = force_sx;
+    if (force_sy > 0 && (force_sy + 2 * pad) * (2 * pad + 1) <= 32) besty = force_sy;
+    if (bestx > h->nx) bestx = h->nx;
+    if (besty > h->ny) besty = h->ny;
+    h->group_cells = bestx;
+    h->group_cells_y = besty;
+    h->gx = (h->nx + bestx - 1) / bestx;
+    const int gy = (h->ny + besty - 1) / besty;
+    h->num_groups = (unsigned long long)h->gx * (unsigned long long)gy * (unsigned long long)h->nz;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -324,9 +352,10 @@ rg_bin_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ targets, Geom<T
         const uint32_t flags = (uint32_t)real_to_bits(w.w);
         const int k1 = 2 * g.rep[1] + 1, k2 = 2 * g.rep[2] + 1;
         const unsigned long long K = (unsigned long long)(2 * g.rep[0] + 1) * k1 * k2;
-        for (int dx = -g.rep[0]; dx <= g.rep[0]; dx++)
-            for (int dy = -g.rep[1]; dy <= g.rep[1]; dy++)
-                for (int dz = -g.rep[2]; dz <= g.rep[2]; dz++) {
+        const int r0 = flags ? g.rep[0] : 0, r1 = flags ? g.rep[1] : 0, r2 = flags ? g.rep[2] : 0;  // interior: own image only
+        for (int dx = -r0; dx <= r0; dx++)
+            for (int dy = -r1; dy <= r1; dy++)
+                for (int dz = -r2; dz <= r2; dz++) {
                     if (!image_needed(flags, dx, dy, dz)) continue;
                     T x, y, z;
                     image_pos(g, w.x, w.y, w.z, dx, dy, dz, x, y, z);
@@ -359,6 +388,11 @@ rg_bin_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ targets, Geom<T
     }
 }
 
+__device__ __forceinline__ uint32_t pack_shift_code(int ex, int ey, int ez)
+{
+    return (uint32_t)(ex + 512) | ((uint32_t)(ey + 512) << 10) | ((uint32_t)(ez + 512) << 20);
+}
+
 // Deterministic order inside each cell (ascending key) and the packed records.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -368,7 +402,7 @@ rg_bin_finalize_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ target
                        const uint32_t* __restrict__ tcstart, const unsigned long long* __restrict__ skey,
                        const uint32_t* __restrict__ scell, const uint32_t* __restrict__ tkey,
                        const uint32_t* __restrict__ tcell, Vec4<T>* __restrict__ spos,
-                       short4* __restrict__ scode, Vec4<T>* __restrict__ tpos, int4* __restrict__ tmeta)
+                       uint32_t* __restrict__ scode, Vec4<T>* __restrict__ tpos, int4* __restrict__ tmeta)
 {
     const DevHeader h = *hp;
     if (h.status & RG_FATAL) return;
@@ -393,9 +427,12 @@ rg_bin_finalize_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ target
         r.w = bits_to_real((int32_t)atom, T());
         spos[b + rank] = r;
         const int ex = dx - ff.x, ey = dy - ff.y, ez = dz - ff.z;
-        if (ex < -32767 || ex > 32767 || ey < -32767 || ey > 32767 || ez < -32767 || ez > 32767)
+        if (ex < -511 || ex > 511 || ey < -511 || ey > 511 || ez < -511 || ez > 511) {
             atomicOr(&hp->status, DYNB_RG_SHIFT_RANGE);
-        scode[b + rank] = make_short4((short)ex, (short)ey, (short)ez, 0);
+            scode[b + rank] = pack_shift_code(0, 0, 0);
+        } else {
+            scode[b + rank] = pack_shift_code(ex, ey, ez);
+        }
     }
     if (j < Nt) {
         const uint32_t c = tcell[j];
@@ -418,9 +455,10 @@ rg_bin_finalize_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ target
 // ------------------------------------------------------------------------------------------
 constexpr int PAIR_WARPS = 8;
 constexpr int PAIR_THREADS = PAIR_WARPS * 32;
-constexpr int PAIR_CAND_BYTES = 6144;  // dense candidate list per warp
-constexpr int PAIR_LIST = 128;         // parked hits per warp
-constexpr int PAIR_WARP_BYTES = PAIR_CAND_BYTES + PAIR_LIST * 2;
+constexpr int PAIR_CAND_BYTES = 5120;  // dense candidate records per warp (320 float4 / 160 double4)
+constexpr int PAIR_CODE_BYTES = 1280;  // packed shift code per candidate (up to 320)
+constexpr int PAIR_LIST = 128;         // parked hits per warp (uint32 each)
+constexpr int PAIR_WARP_BYTES = PAIR_CAND_BYTES + PAIR_CODE_BYTES + PAIR_LIST * 4;
 
 enum { MODE_COUNT = 0, MODE_FILL = 1, MODE_HALO = 2 };
 
@@ -440,7 +478,7 @@ template <typename T> struct PairParams {
     const uint32_t* cstart;
     const uint32_t* tcstart;
     const Vec4<T>* spos;
-    const short4* scode;
+    const uint32_t* scode;    // packed (shift - floor(frac) of the source atom), 10 bits per axis, bias 512
     const Vec4<T>* tpos;
     const int4* tmeta;
     uint32_t* tcount;         // [Nt+1] degree per sorted target; running cursor in FILL
@@ -453,7 +491,7 @@ constexpr int64_t RG_PARAMS_OFFSET = 512;
 constexpr int64_t RG_HEADER_BYTES = 1024;
 
 template <typename T, int MODE>
-__global__ void __launch_bounds__(PAIR_THREADS)
+__global__ void __launch_bounds__(PAIR_THREADS, 4)
 rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restrict__ ei, float* __restrict__ shifts,
                T* __restrict__ d2out, const long long E, const HaloArgs halo)
 {
@@ -461,32 +499,47 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
     extern __shared__ __align__(32) unsigned char smem_raw[];
     constexpr int CAP = PAIR_CAND_BYTES / (int)sizeof(Vec4<T>);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    Vec4<T>* cand = reinterpret_cast<Vec4<T>*>(smem_raw + warp * PAIR_WARP_BYTES);
-    unsigned short* list = reinterpret_cast<unsigned short*>(smem_raw + warp * PAIR_WARP_BYTES + PAIR_CAND_BYTES);
+    unsigned char* wbase = smem_raw + warp * PAIR_WARP_BYTES;
+    Vec4<T>* cand = reinterpret_cast<Vec4<T>*>(wbase);
+    uint32_t* codes = reinterpret_cast<uint32_t*>(wbase + PAIR_CAND_BYTES);
+    uint32_t* list = reinterpret_cast<uint32_t*>(wbase + PAIR_CAND_BYTES + PAIR_CODE_BYTES);
 
-    const DevHeader h = *p.h;
-    if (h.status & RG_FATAL) return;
-    const int nx = h.nx, ny = h.ny, nz = h.nz, S = h.group_cells, gx = h.gx, pad = h.pad;
-    const int Wd = 2 * pad + 1, nrun = Wd * Wd;
+    const DevHeader* hp = p.h;
+    if (hp->status & RG_FATAL) return;
+    const int nx = hp->nx, ny = hp->ny, nz = hp->nz, S = hp->group_cells, Sy = hp->group_cells_y, pad = hp->pad;
+    const uint32_t gx = (uint32_t)hp->gx;
+    const uint32_t gy = (uint32_t)((ny + Sy - 1) / Sy);
+    const uint32_t num_groups = (uint32_t)hp->num_groups;  // < 2^31: never more groups than cells
+    const int Wd = 2 * pad + 1, Wy = Sy + 2 * pad, nrun = Wy * Wd;
+    const int lane_dy = (lane % Wy) - pad, lane_dz = (lane / Wy) - pad;
+    const int sub = lane >> 3, sl = lane & 7;
     const T r2 = p.r2;
     const T eps = (T)1e-8f;
     const uint32_t lt = lanemask_lt();
 
-    const unsigned long long nwarps = (unsigned long long)gridDim.x * PAIR_WARPS;
-    for (unsigned long long grp = (unsigned long long)blockIdx.x * PAIR_WARPS + warp; grp < h.num_groups; grp += nwarps) {
-        const int ix = (int)(grp % (unsigned long long)gx);
-        const unsigned long long row = grp / (unsigned long long)gx;
-        const int cy = (int)(row % (unsigned long long)ny), cz = (int)(row / (unsigned long long)ny);
+    const uint32_t nwarps = gridDim.x * PAIR_WARPS;
+    for (uint32_t grp = blockIdx.x * PAIR_WARPS + warp; grp < num_groups; grp += nwarps) {
+        const uint32_t row = grp / gx;
+        const int ix = (int)(grp - row * gx);
+        const int cz = (int)(row / gy), iy = (int)(row - (uint32_t)cz * gy);
         const int cx0 = ix * S, cx1 = min(cx0 + S, nx) - 1;
-        const uint32_t cbase = ((uint32_t)cz * ny + cy) * nx;
-        const uint32_t t0 = p.tcstart[cbase + cx0], t1 = p.tcstart[cbase + cx1 + 1];
-        if (t0 == t1) continue;
+        const int cy0 = iy * Sy, cy1 = min(cy0 + Sy, ny) - 1;
+        // targets: one contiguous run per target row
+        uint32_t tb[2], te[2];
+        tb[0] = p.tcstart[((uint32_t)cz * ny + cy0) * nx + cx0];
+        te[0] = p.tcstart[((uint32_t)cz * ny + cy0) * nx + cx1 + 1];
+        tb[1] = te[1] = 0;
+        if (cy1 > cy0) {
+            tb[1] = p.tcstart[((uint32_t)cz * ny + cy1) * nx + cx0];
+            te[1] = p.tcstart[((uint32_t)cz * ny + cy1) * nx + cx1 + 1];
+        }
+        if (tb[0] == te[0] && tb[1] == te[1]) continue;
 
-        // contiguous source runs: lane r owns run (dy, dz)
+        // contiguous source runs: lane r owns run (y row, z row)
         int run_a = 0, run_len = 0;
         if (lane < nrun) {
-            const int yy = cy + (lane % Wd) - pad, zz = cz + (lane / Wd) - pad;
-            if (yy >= 0 && yy < ny && zz >= 0 && zz < nz) {
+            const int yy = cy0 + lane_dy, zz = cz + lane_dz;
+            if (yy >= 0 && yy < ny && yy <= cy1 + pad && zz >= 0 && zz < nz) {
                 const uint32_t b = ((uint32_t)zz * ny + yy) * nx;
                 const uint32_t a = p.cstart[b + max(cx0 - pad, 0)];
                 const uint32_t e = p.cstart[b + min(cx1 + pad, nx - 1) + 1];
@@ -500,8 +553,10 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
         for (int cbeg = 0, chunk = 0; cbeg < L; cbeg += CAP, chunk++) {
             const int clen = min(CAP, L - cbeg);
             const int clen32 = (clen + 31) & ~31;
+            const bool more_chunks = cbeg + CAP < L;
             __syncwarp();
-            // dense staging: slot j holds the record of flattened candidate cbeg + j
+            // dense staging: slot j of the list holds flattened candidate cbeg + j; every lane finds the
+            // run of its candidate by a shuffle binary search, so all loads of a chunk are independent
             for (int j = lane; j < clen32; j += 32) {
                 const int jj = cbeg + j;
                 int r = 0;
@@ -511,98 +566,142 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                     const int o = __shfl_sync(0xffffffffu, run_off, cr & 31);
                     if (cr < 32 && o <= jj) r = cr;
                 }
-                const int ra = __shfl_sync(0xffffffffu, run_a, r);
-                const int ro = __shfl_sync(0xffffffffu, run_off, r);
-                Vec4<T> c;
+                const int gidx = __shfl_sync(0xffffffffu, run_a, r) + (jj - __shfl_sync(0xffffffffu, run_off, r));
                 if (j < clen) {
-                    const int gidx = ra + (jj - ro);
-                    c = p.spos[gidx];
-                    if (MODE == MODE_FILL) c.w = bits_to_real((int32_t)gidx, T());
-                } else {
-                    c.x = c.y = c.z = (T)3.0e38f;  // never within the cutoff
-                    c.w = (T)0;
+                    cand[j] = p.spos[gidx];  // w = atom id
+                    if (MODE == MODE_FILL) codes[j] = p.scode[gidx];
                 }
-                cand[j] = c;
+            }
+            if (clen + lane < clen32) {
+                Vec4<T> c;
+                c.x = c.y = c.z = (T)3.0e38f;  // never within the cutoff
+                c.w = (T)0;
+                cand[clen + lane] = c;
             }
             __syncwarp();
 
-            for (uint32_t t = t0; t < t1; t++) {
-                const Vec4<T> tp = p.tpos[t];
-                const T tx = tp.x, ty = tp.y, tz = tp.z;
-                int produced = (chunk == 0 || MODE == MODE_HALO) ? 0 : (int)p.tcount[t];
-                int cnt = 0;
-                int4 tm;
-                long long base = 0;
-                long long owner_t = 0;
-                bool foreign = false;
-                if (MODE == MODE_FILL) {
-                    tm = p.tmeta[t];
-                    base = p.toffset[t];
-                }
-                if (MODE == MODE_HALO) {
-                    tm = p.tmeta[t];
-                    owner_t = halo.owner[tm.x];
-                }
-                for (int k = 0; k < clen32; k += 32) {
-                    const int j = k + lane;
-                    const Vec4<T> c = cand[j];
-                    const T sx = c.x, sy = c.y, sz = c.z;
-                    const T d2 = (tx - sx) * (tx - sx) + (ty - sy) * (ty - sy) + (tz - sz) * (tz - sz);
-                    const bool hit = (d2 <= r2) && (d2 > eps);
-                    const uint32_t mask = __ballot_sync(0xffffffffu, hit);
-                    if (MODE == MODE_FILL) {
-                        if (hit) list[cnt + __popc(mask & lt)] = (unsigned short)j;
-                    }
-                    cnt += __popc(mask);
-                    if (MODE == MODE_HALO) {
-                        if (hit) {
-                            const int a = real_to_bits(c.w);
-                            if (halo.owner[a] != owner_t) {
-                                uint32_t* wd = &halo.needed[(long long)a * halo.words + (owner_t >> 5)];
-                                const uint32_t bit = 1u << (owner_t & 31);
-                                if (!(*wd & bit)) atomicOr(wd, bit);
-                                foreign = true;
-                            }
-                        }
-                    }
-                    if (MODE == MODE_FILL) {
-                        if (cnt > PAIR_LIST - 32 || k + 32 >= clen32) {
-                            __syncwarp();
-                            for (int i = lane; i < cnt; i += 32) {
-                                const int jh = list[i];
-                                const Vec4<T> ch = cand[jh];
-                                const int gidx = real_to_bits(ch.w);
-                                const int atom = real_to_bits(p.spos[gidx].w);
-                                const short4 code = p.scode[gidx];
-                                const long long e = base + produced + i;
-                                ei[e] = (long long)atom;
-                                ei[E + e] = (long long)tm.x;
-                                shifts[3 * e + 0] = (float)((int)code.x + tm.y);
-                                shifts[3 * e + 1] = (float)((int)code.y + tm.z);
-                                shifts[3 * e + 2] = (float)((int)code.z + tm.w);
-                                if (d2out != nullptr) {
-                                    const T hx = ch.x, hy = ch.y, hz = ch.z;
-                                    d2out[e] = (tx - hx) * (tx - hx) + (ty - hy) * (ty - hy) + (tz - hz) * (tz - hz);
-                                }
-                            }
-                            produced += cnt;
-                            cnt = 0;
-                            __syncwarp();
-                        }
-                    }
+#pragma unroll
+          for (int yr = 0; yr < 2; yr++) {
+            const uint32_t t0 = tb[yr], t1 = te[yr];
+            // two targets share every candidate load
+            for (uint32_t t = t0; t < t1; t += 2) {
+                const bool has2 = (t + 1 < t1);
+                const Vec4<T> tpA = p.tpos[t];
+                const Vec4<T> tpB = p.tpos[has2 ? t + 1 : t];
+                const T ax = tpA.x, ay = tpA.y, az = tpA.z, bx = tpB.x, by = tpB.y, bz = tpB.z;
+                int prodA = 0, prodB = 0;
+                if (chunk != 0 && MODE != MODE_HALO) {
+                    prodA = (int)p.tcount[t];
+                    prodB = has2 ? (int)p.tcount[t + 1] : 0;
                 }
                 if (MODE == MODE_COUNT) {
-                    if (lane == 0) p.tcount[t] = (uint32_t)(produced + cnt);
-                } else if (MODE == MODE_FILL) {
-                    if (lane == 0 && cbeg + CAP < L) p.tcount[t] = (uint32_t)produced;
+                    int ca = 0, cb = 0;
+#pragma unroll 2
+                    for (int k = 0; k < clen32; k += 32) {
+                        const Vec4<T> c = cand[k + lane];
+                        const T sx = c.x, sy = c.y, sz = c.z;
+                        const T dA = (ax - sx) * (ax - sx) + (ay - sy) * (ay - sy) + (az - sz) * (az - sz);
+                        const T dB = (bx - sx) * (bx - sx) + (by - sy) * (by - sy) + (bz - sz) * (bz - sz);
+                        ca += ((dA <= r2) && (dA > eps)) ? 1 : 0;
+                        cb += ((dB <= r2) && (dB > eps)) ? 1 : 0;
+                    }
+                    ca = __reduce_add_sync(0xffffffffu, ca);
+                    cb = __reduce_add_sync(0xffffffffu, cb);
+                    if (lane == 0) {
+                        p.tcount[t] = (uint32_t)(prodA + ca);
+                        if (has2) p.tcount[t + 1] = (uint32_t)(prodB + cb);
+                    }
                 } else {
-                    if (__any_sync(0xffffffffu, foreign) && lane == 0) halo.has_foreign[tm.x] = 1;
+                    int4 tmA = p.tmeta[t];
+                    int4 tmB = p.tmeta[has2 ? t + 1 : t];
+                    long long baseA = 0, baseB = 0, ownA = 0, ownB = 0;
+                    bool foreignA = false, foreignB = false;
+                    if (MODE == MODE_FILL) {
+                        baseA = p.toffset[t];
+                        baseB = p.toffset[has2 ? t + 1 : t];
+                    } else {
+                        ownA = halo.owner[tmA.x];
+                        ownB = halo.owner[tmB.x];
+                    }
+                    int n = 0;  // parked entries
+                    for (int k = 0; k < clen32; k += 32) {
+                        const int j = k + lane;
+                        const Vec4<T> c = cand[j];
+                        const T sx = c.x, sy = c.y, sz = c.z;
+                        const T dA = (ax - sx) * (ax - sx) + (ay - sy) * (ay - sy) + (az - sz) * (az - sz);
+                        const T dB = (bx - sx) * (bx - sx) + (by - sy) * (by - sy) + (bz - sz) * (bz - sz);
+                        const bool hitA = (dA <= r2) && (dA > eps);
+                        const bool hitB = has2 && (dB <= r2) && (dB > eps);
+                        if (MODE == MODE_HALO) {
+                            if (hitA || hitB) {
+                                const int a = real_to_bits(c.w);
+                                const long long oa = halo.owner[a];
+                                if (hitA && oa != ownA) {
+                                    uint32_t* wd = &halo.needed[(long long)a * halo.words + (ownA >> 5)];
+                                    const uint32_t bit = 1u << (ownA & 31);
+                                    if (!(*wd & bit)) atomicOr(wd, bit);
+                                    foreignA = true;
+                                }
+                                if (hitB && oa != ownB) {
+                                    uint32_t* wd = &halo.needed[(long long)a * halo.words + (ownB >> 5)];
+                                    const uint32_t bit = 1u << (ownB & 31);
+                                    if (!(*wd & bit)) atomicOr(wd, bit);
+                                    foreignB = true;
+                                }
+                            }
+                        } else {
+                            const uint32_t mA = __ballot_sync(0xffffffffu, hitA);
+                            const uint32_t mB = __ballot_sync(0xffffffffu, hitB);
+                            const int nA = __popc(mA);
+                            // entry: candidate slot (10 bits) | target select (1 bit) | position inside the target's edge run
+                            if (hitA) list[n + __popc(mA & lt)] = (uint32_t)j | ((uint32_t)(prodA + __popc(mA & lt)) << 11);
+                            if (hitB) list[n + nA + __popc(mB & lt)] = (uint32_t)j | (1u << 10) | ((uint32_t)(prodB + __popc(mB & lt)) << 11);
+                            prodA += nA;
+                            prodB += __popc(mB);
+                            n += nA + __popc(mB);
+                            if (n > PAIR_LIST - 64 || k + 32 >= clen32) {
+                                __syncwarp();
+                                for (int i = lane; i < n; i += 32) {
+                                    const uint32_t ent = list[i];
+                                    const int jh = (int)(ent & 1023u);
+                                    const bool selB = (ent >> 10) & 1u;
+                                    const Vec4<T> ch = cand[jh];
+                                    const uint32_t code = codes[jh];
+                                    const int4 tm = selB ? tmB : tmA;
+                                    const long long e = (selB ? baseB : baseA) + (long long)(ent >> 11);
+                                    ei[e] = (long long)real_to_bits(ch.w);
+                                    ei[E + e] = (long long)tm.x;
+                                    shifts[3 * e + 0] = (float)((int)(code & 1023u) - 512 + tm.y);
+                                    shifts[3 * e + 1] = (float)((int)((code >> 10) & 1023u) - 512 + tm.z);
+                                    shifts[3 * e + 2] = (float)((int)((code >> 20) & 1023u) - 512 + tm.w);
+                                    if (d2out != nullptr) {
+                                        const T tx = selB ? bx : ax, ty = selB ? by : ay, tz = selB ? bz : az;
+                                        const T hx = ch.x, hy = ch.y, hz = ch.z;
+                                        d2out[e] = (tx - hx) * (tx - hx) + (ty - hy) * (ty - hy) + (tz - hz) * (tz - hz);
+                                    }
+                                }
+                                n = 0;
+                                __syncwarp();
+                            }
+                        }
+                    }
+                    if (MODE == MODE_FILL) {
+                        if (more_chunks && lane == 0) {
+                            p.tcount[t] = (uint32_t)prodA;
+                            if (has2) p.tcount[t + 1] = (uint32_t)prodB;
+                        }
+                    } else {
+                        if (__any_sync(0xffffffffu, foreignA) && lane == 0) halo.has_foreign[tmA.x] = 1;
+                        if (has2 && __any_sync(0xffffffffu, foreignB) && lane == 0) halo.has_foreign[tmB.x] = 1;
+                    }
                 }
             }
+          }
         }
         // a group whose neighbourhood holds no source at all still owes its targets a zero
         if (MODE == MODE_COUNT && L == 0) {
-            for (uint32_t t = t0 + lane; t < t1; t += 32) p.tcount[t] = 0;
+            for (int yr = 0; yr < 2; yr++)
+                for (uint32_t t = tb[yr] + lane; t < te[yr]; t += 32) p.tcount[t] = 0;
         }
     }
 }
@@ -656,7 +755,7 @@ static RgLayout rg_layout(int64_t N, int64_t Nt, int64_t src_cap, int64_t cell_c
     L.skey = take(src_cap * 8);
     L.scell = take(src_cap * 4);
     L.spos = take(src_cap * v4);
-    L.scode = take(src_cap * 8);
+    L.scode = take(src_cap * 4);
     L.tkey = take(Nt * 4);
     L.tcell = take(Nt * 4);
     L.tpos = take(Nt * v4);
@@ -777,7 +876,7 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
     auto* skey = reinterpret_cast<unsigned long long*>(w + L.skey);
     auto* scell = reinterpret_cast<uint32_t*>(w + L.scell);
     auto* spos = reinterpret_cast<Vec4<T>*>(w + L.spos);
-    auto* scode = reinterpret_cast<short4*>(w + L.scode);
+    auto* scode = reinterpret_cast<uint32_t*>(w + L.scode);
     auto* tkey = reinterpret_cast<uint32_t*>(w + L.tkey);
     auto* tcell = reinterpret_cast<uint32_t*>(w + L.tcell);
     auto* tpos = reinterpret_cast<Vec4<T>*>(w + L.tpos);
@@ -812,7 +911,13 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
     const int vec_ok = (reinterpret_cast<uintptr_t>(pos_dev) % 16 == 0) ? 1 : 0;
     rg_wrap_kernel<T><<<(unsigned)((N + WRAP_THREADS - 1) / WRAP_THREADS), WRAP_THREADS, 0, stream>>>(
         static_cast<const T*>(pos_dev), N, g, vec_ok, posw, aff, h);
-    rg_grid_kernel<T><<<1, 32, 0, stream>>>(h, radius, (long long)src_cap, (long long)cell_cap);
+    // tuning knob: DYNB_RG_GROUP="sx,sy" forces the cells per warp work item (default: chosen on the device)
+    int force_sx = 0, force_sy = 0;
+    if (const char* env = getenv("DYNB_RG_GROUP")) sscanf(env, "%d,%d", &force_sx, &force_sy);
+    if (force_sx < 0 || force_sx > 8) force_sx = 0;
+    if (force_sy < 0 || force_sy > 2) force_sy = 0;
+    rg_grid_kernel<T><<<1, 32, 0, stream>>>(h, radius, (long long)src_cap, (long long)cell_cap,
+                                            PAIR_CAND_BYTES / (int)sizeof(Vec4<T>), force_sx, force_sy);
 
     const int64_t nb = std::max(N, Nt);
     rg_bin_kernel<T, false><<<(unsigned)((nb + 255) / 256), 256, 0, stream>>>(

@@ -155,7 +155,7 @@ def plan_radius_graph(pos, cell, pbc, radius, target_indices=None) -> RadiusGrap
     if status & _lib.RG_NONFINITE:
         raise RuntimeError("pos contains NaN or Inf")
     if status & _lib.RG_SHIFT_RANGE:
-        raise RuntimeError("an atom lies too many periodic cells outside the unit cell (limit 32767)")
+        raise RuntimeError("an atom lies too many periodic cells outside the unit cell (limit 511)")
     if status & _lib.RG_SRC_OVERFLOW:
         raise RuntimeError("periodic-image capacity overflow")
     plan = RadiusGraphPlan()

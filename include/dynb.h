@@ -36,7 +36,7 @@ extern "C" {
 /* Bits of dynb_rg_header.status (set by kernels, read by the host after the plan). */
 #define DYNB_RG_SRC_OVERFLOW 1u    /* more periodic images than src_capacity: re-plan with header.M */
 #define DYNB_RG_BAD_TARGET 2u      /* a target index outside [0, n_atoms) */
-#define DYNB_RG_SHIFT_RANGE 4u     /* an atom lies more than 32767 cells outside the unit cell */
+#define DYNB_RG_SHIFT_RANGE 4u     /* an atom lies more than 511 cells outside the unit cell */
 #define DYNB_RG_NONFINITE 8u       /* a position is NaN or Inf */
 
 const char* dynb_last_error(void);
