@@ -139,7 +139,7 @@ constexpr int WRAP_THREADS = 256;
 template <typename T>
 __global__ void __launch_bounds__(WRAP_THREADS)
 rg_wrap_kernel(const T* __restrict__ pos, int64_t N, Geom<T> g, int vec_ok, Vec4<T>* __restrict__ posw,
-               int4* __restrict__ aff, DevHeader* __restrict__ h)
+               int4* __restrict__ aff, DevHeader* __restrict__ h, unsigned long long* __restrict__ partials)
 {
     __shared__ T stage[WRAP_THREADS * 3];
     __shared__ unsigned long long red[6][WRAP_THREADS / 32];
@@ -242,16 +242,17 @@ rg_wrap_kernel(const T* __restrict__ pos, int64_t N, Geom<T> g, int vec_ok, Vec4
         if (status) atomicOr(&h->status, status);
     }
     __syncthreads();
+    // per-block partial results (bounding box, image count); rg_grid_kernel reduces them, so that no
+    // block contends for a handful of header words
     if (threadIdx.x < 6) {
         unsigned long long v = red[threadIdx.x][0];
         for (int w = 1; w < WRAP_THREADS / 32; w++)
             v = (threadIdx.x < 3) ? min(v, red[threadIdx.x][w]) : max(v, red[threadIdx.x][w]);
-        if (threadIdx.x < 3) atomicMin(&h->bb_min[threadIdx.x], v);
-        else atomicMax(&h->bb_max[threadIdx.x - 3], v);
+        partials[(size_t)blockIdx.x * 8 + threadIdx.x] = v;
     } else if (threadIdx.x == 6) {
         unsigned long long c = 0;
         for (int w = 0; w < WRAP_THREADS / 32; w++) c += red_cnt[w];
-        if (c) atomicAdd(&h->M, c);
+        partials[(size_t)blockIdx.x * 8 + 6] = c;
     }
 }
 
@@ -261,9 +262,42 @@ rg_wrap_kernel(const T* __restrict__ pos, int64_t N, Geom<T> g, int vec_ok, Vec4
 // grow, and once they are wider than the cutoff the scan shrinks to +-1.
 // ------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void rg_grid_kernel(DevHeader* h, double radius, long long src_capacity, long long cell_capacity, int cand_capacity,
-               int force_sx, int force_sy)
+__global__ void __launch_bounds__(256)
+rg_grid_kernel(DevHeader* h, double radius, long long src_capacity, long long cell_capacity, int cand_capacity,
+               int force_sx, int force_sy, const unsigned long long* __restrict__ partials, int num_partials)
 {
+    {   // reduce the per-block partials of rg_wrap_kernel into the header
+        __shared__ unsigned long long red[7][8];
+        unsigned long long v[7] = {~0ull, ~0ull, ~0ull, 0ull, 0ull, 0ull, 0ull};
+        for (int b = threadIdx.x; b < num_partials; b += blockDim.x) {
+#pragma unroll
+            for (int k = 0; k < 3; k++) {
+                v[k] = min(v[k], partials[(size_t)b * 8 + k]);
+                v[3 + k] = max(v[3 + k], partials[(size_t)b * 8 + 3 + k]);
+            }
+            v[6] += partials[(size_t)b * 8 + 6];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+            for (int k = 0; k < 3; k++) {
+                v[k] = min(v[k], __shfl_xor_sync(0xffffffffu, v[k], o));
+                v[3 + k] = max(v[3 + k], __shfl_xor_sync(0xffffffffu, v[3 + k], o));
+            }
+            v[6] += __shfl_xor_sync(0xffffffffu, v[6], o);
+        }
+        if ((threadIdx.x & 31) == 0)
+            for (int k = 0; k < 7; k++) red[k][threadIdx.x >> 5] = v[k];
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int k = 0; k < 7; k++) {
+                unsigned long long a = red[k][0];
+                for (int w = 1; w < (int)(blockDim.x >> 5); w++)
+                    a = (k < 3) ? min(a, red[k][w]) : (k < 6 ? max(a, red[k][w]) : a + red[k][w]);
+                if (k < 3) h->bb_min[k] = a; else if (k < 6) h->bb_max[k - 3] = a; else h->M = a;
+            }
+        }
+    }
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     if (h->M > (unsigned long long)src_capacity) h->status |= DYNB_RG_SRC_OVERFLOW;
     if (h->M == 0 || (h->status & RG_FATAL)) {
@@ -308,19 +342,17 @@ __global__ void rg_grid_kernel(DevHeader* h, double radius, long long src_capaci
     // cells per warp work item (Sx along x, Sy along y): as many target cells as possible while the
     // expected dense candidate list stays within 1.5 shared-memory lists
     const double avg = (double)h->M / (double)ncell;
-    const double budget = 1.5 * (double)cand_capacity;  // a second chunk costs less than smaller groups (measured)
+    // measured on B200 (1 M-atom liquid, 1 M-atom fcc): 2 x 2 cells per warp is best even when the
+    // candidate list then needs a second chunk; fall back to 2 x 1 and 1 x 1 for denser cells
+    const double budget = 1.5 * (double)cand_capacity;
+    const int shapes[3][2] = {{2, 2}, {2, 1}, {1, 1}};
     int bestx = 1, besty = 1;
-    double best_per_target = 1e300;
-    for (int sy = 1; sy <= 2; sy++)
-        for (int sx = 1; sx <= 4; sx++) {
-            if ((sy + 2 * pad) * (2 * pad + 1) > 32) continue;  // one lane per candidate run
-            const double Lexp = (double)(sx + 2 * pad) * (double)(sy + 2 * pad) * (double)(2 * pad + 1) * (avg > 1e-6 ? avg : 1e-6);
-            if (Lexp > budget && !(sx == 1 && sy == 1)) continue;
-            const int cells = sx * sy;
-            if (cells > bestx * besty || (cells == bestx * besty && Lexp / cells < best_per_target)) {
-                bestx = sx; besty = sy; best_per_target = Lexp / cells;
-            }
-        }
+    for (int c = 0; c < 3; c++) {
+        const int sx = shapes[c][0], sy = shapes[c][1];
+        if ((sy + 2 * pad) * (2 * pad + 1) > 32) continue;  // one lane per candidate run
+        const double Lexp = (double)(sx + 2 * pad) * (double)(sy + 2 * pad) * (double)(2 * pad + 1) * (avg > 1e-6 ? avg : 1e-6);
+        if (Lexp <= budget || c == 2) { bestx = sx; besty = sy; break; }
+    }
     if (force_sx > 0) bestx = force_sx;
     if (force_sy > 0 && (force_sy + 2 * pad) * (2 * pad + 1) <= 32) besty = force_sy;
     if (bestx > h->nx) bestx = h->nx;
@@ -719,9 +751,15 @@ rg_post_count_kernel(int64_t Nt, const Vec4<T>* __restrict__ tpos, const uint32_
         c = tcount[k];
         if (counts_out != nullptr) counts_out[real_to_bits(tpos[k].w)] = (int32_t)c;
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) c = max(c, __shfl_xor_sync(0xffffffffu, c, o));
-    if ((threadIdx.x & 31) == 0 && c > 0) atomicMax(&h->max_degree, c);
+    __shared__ uint32_t wmax[8];
+    c = __reduce_max_sync(0xffffffffu, c);
+    if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t m = 0;
+        for (int w = 0; w < 8; w++) m = max(m, wmax[w]);
+        if (m > 0) atomicMax(&h->max_degree, m);
+    }
 }
 
 __global__ void rg_zero_counts_kernel(int64_t Nt, int32_t* counts_out)
@@ -734,7 +772,7 @@ __global__ void rg_zero_counts_kernel(int64_t Nt, int32_t* counts_out)
 // host side
 // ------------------------------------------------------------------------------------------
 struct RgLayout {
-    int64_t hdr, posw, aff, ccount, cfill, tccount, tcfill, skey, scell, spos, scode, tkey, tcell, tpos, tmeta,
+    int64_t hdr, partials, posw, aff, ccount, cfill, tccount, tcfill, skey, scell, spos, scode, tkey, tcell, tpos, tmeta,
         tcount, toffset, sums, total;
 };
 
@@ -750,6 +788,7 @@ static RgLayout rg_layout(int64_t N, int64_t Nt, int64_t src_cap, int64_t cell_c
     L.cfill = take((cell_cap + 2) * 4);
     L.tccount = take((cell_cap + 2) * 4);
     L.tcfill = take((cell_cap + 2) * 4);
+    L.partials = take(((N + 255) / 256 + 1) * 64);
     L.posw = take(N * v4);
     L.aff = take(N * 16);
     L.skey = take(src_cap * 8);
@@ -903,21 +942,23 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
     }
     // Small pageable source: cudaMemcpyAsync stages it before returning, so the stack buffer may die.
     DYNB_CUDA_OK(cudaMemcpyAsync(w + L.hdr, init, sizeof(init), cudaMemcpyHostToDevice, stream));
-    DYNB_CUDA_OK(cudaMemsetAsync(w + L.ccount, 0, (size_t)(L.posw - L.ccount), stream));
+    DYNB_CUDA_OK(cudaMemsetAsync(w + L.ccount, 0, (size_t)(L.partials - L.ccount), stream));
     DYNB_CUDA_OK(cudaMemsetAsync(w + L.tcount, 0, (size_t)((Nt + 1) * 4), stream));
     if (counts_out != nullptr && Nt > 0)
         rg_zero_counts_kernel<<<(unsigned)((Nt + 255) / 256), 256, 0, stream>>>(Nt, counts_out);
 
     const int vec_ok = (reinterpret_cast<uintptr_t>(pos_dev) % 16 == 0) ? 1 : 0;
     rg_wrap_kernel<T><<<(unsigned)((N + WRAP_THREADS - 1) / WRAP_THREADS), WRAP_THREADS, 0, stream>>>(
-        static_cast<const T*>(pos_dev), N, g, vec_ok, posw, aff, h);
+        static_cast<const T*>(pos_dev), N, g, vec_ok, posw, aff, h, reinterpret_cast<unsigned long long*>(w + L.partials));
     // tuning knob: DYNB_RG_GROUP="sx,sy" forces the cells per warp work item (default: chosen on the device)
     int force_sx = 0, force_sy = 0;
     if (const char* env = getenv("DYNB_RG_GROUP")) sscanf(env, "%d,%d", &force_sx, &force_sy);
     if (force_sx < 0 || force_sx > 8) force_sx = 0;
     if (force_sy < 0 || force_sy > 2) force_sy = 0;
-    rg_grid_kernel<T><<<1, 32, 0, stream>>>(h, radius, (long long)src_cap, (long long)cell_cap,
-                                            PAIR_CAND_BYTES / (int)sizeof(Vec4<T>), force_sx, force_sy);
+    rg_grid_kernel<T><<<1, 256, 0, stream>>>(h, radius, (long long)src_cap, (long long)cell_cap,
+                                             PAIR_CAND_BYTES / (int)sizeof(Vec4<T>), force_sx, force_sy,
+                                             reinterpret_cast<const unsigned long long*>(w + L.partials),
+                                             (int)((N + WRAP_THREADS - 1) / WRAP_THREADS));
 
     const int64_t nb = std::max(N, Nt);
     rg_bin_kernel<T, false><<<(unsigned)((nb + 255) / 256), 256, 0, stream>>>(

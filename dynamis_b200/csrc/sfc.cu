@@ -40,12 +40,17 @@ sfc_minmax_kernel(const float* __restrict__ pos, int64_t n, SfcBounds* __restric
             mn[k] = min(mn[k], __shfl_xor_sync(0xffffffffu, mn[k], o));
             mx[k] = max(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], o));
         }
+    __shared__ uint32_t red[6][8];
     if ((threadIdx.x & 31) == 0) {
 #pragma unroll
-        for (int k = 0; k < 3; k++) {
-            atomicMin(&b->mn[k], mn[k]);
-            atomicMax(&b->mx[k], mx[k]);
-        }
+        for (int k = 0; k < 3; k++) { red[k][threadIdx.x >> 5] = mn[k]; red[3 + k][threadIdx.x >> 5] = mx[k]; }
+    }
+    __syncthreads();
+    if (threadIdx.x < 6) {  // one atomic per block and bound, not one per warp
+        uint32_t v = red[threadIdx.x][0];
+        for (int w = 1; w < 8; w++) v = (threadIdx.x < 3) ? min(v, red[threadIdx.x][w]) : max(v, red[threadIdx.x][w]);
+        if (threadIdx.x < 3) atomicMin(&b->mn[threadIdx.x], v);
+        else atomicMax(&b->mx[threadIdx.x - 3], v);
     }
 }
 
@@ -117,7 +122,7 @@ sfc_keys_kernel(const float* __restrict__ pos, int64_t n, const SfcBounds* __res
 
 // ------------------------------------------------------------------------------------------ radix sort
 constexpr int RS_THREADS = 256;
-constexpr int RS_ITEMS = 8;
+constexpr int RS_ITEMS = 4;  // 1024 keys per block: enough blocks to fill the GPU at 1 M keys
 constexpr int RS_TILE = RS_THREADS * RS_ITEMS;
 constexpr int RS_WARPS = RS_THREADS / 32;
 
@@ -315,7 +320,7 @@ static int sfc_keys_into(const float* pos, int64_t n, int curve, unsigned char* 
     for (int k = 0; k < 3; k++) { init.mn[k] = 0xffffffffu; init.mx[k] = 0u; init.pmin[k] = 0.f; init.prange[k] = 1.f; }
     SfcBounds* b = reinterpret_cast<SfcBounds*>(ws + L.bounds);
     DYNB_CUDA_OK(cudaMemcpyAsync(b, &init, sizeof(init), cudaMemcpyHostToDevice, stream));
-    const int grid = (int)std::min<int64_t>((n + 255) / 256, (int64_t)sm_count_cached() * 8);
+    const int grid = (int)std::min<int64_t>((n + 255) / 256, (int64_t)sm_count_cached() * 4);
     sfc_minmax_kernel<<<grid, 256, 0, stream>>>(pos, n, b);
     sfc_bounds_finish_kernel<<<1, 32, 0, stream>>>(b);
     const unsigned nbk = (unsigned)((n + 255) / 256);
