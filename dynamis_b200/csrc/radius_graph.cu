@@ -58,6 +58,8 @@ struct DevHeader {
     unsigned long long bb_max[3];
     double gmin[3];
     double res_inv;
+    double clip_lo[3];  // source images outside [clip_lo, clip_hi] cannot reach any target and are dropped
+    double clip_hi[3];
 };
 static_assert(offsetof(DevHeader, ncell_plus1) == sizeof(dynb_rg_header), "public header prefix mismatch");
 
@@ -256,6 +258,44 @@ rg_wrap_kernel(const T* __restrict__ pos, int64_t N, Geom<T> g, int vec_ok, Vec4
     }
 }
 
+// Bounding box of the wrapped TARGET positions (only when a target subset is given): per-block
+// partials, reduced by rg_grid_kernel.  Sources farther than the cutoff from that box are never
+// needed, which keeps the grid and the image count small when a rank builds edges for its own
+// atoms only.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rg_target_bbox_kernel(const int64_t* __restrict__ targets, int64_t Nt, int64_t N, const Vec4<T>* __restrict__ posw,
+                      unsigned long long* __restrict__ partials)
+{
+    __shared__ unsigned long long red[6][8];
+    unsigned long long v[6] = {~0ull, ~0ull, ~0ull, 0ull, 0ull, 0ull};
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < Nt) {
+        const int64_t a = targets[i];
+        if (a >= 0 && a < N) {
+            const Vec4<T> w = posw[a];
+            v[0] = v[3] = ordered_any(w.x);
+            v[1] = v[4] = ordered_any(w.y);
+            v[2] = v[5] = ordered_any(w.z);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            v[k] = min(v[k], __shfl_xor_sync(0xffffffffu, v[k], o));
+            v[3 + k] = max(v[3 + k], __shfl_xor_sync(0xffffffffu, v[3 + k], o));
+        }
+    if ((threadIdx.x & 31) == 0)
+        for (int k = 0; k < 6; k++) red[k][threadIdx.x >> 5] = v[k];
+    __syncthreads();
+    if (threadIdx.x < 6) {
+        unsigned long long a = red[threadIdx.x][0];
+        for (int w = 1; w < 8; w++) a = (threadIdx.x < 3) ? min(a, red[threadIdx.x][w]) : max(a, red[threadIdx.x][w]);
+        partials[(size_t)blockIdx.x * 8 + threadIdx.x] = a;
+    }
+}
+
 // ------------------------------------------------------------------------------------------
 // rg_grid: one thread chooses the grid.  Cells of edge radius/1.99 scanned +-2 (as the
 // reference, :662,776) unless that would need more than cell_capacity cells; then the cells
@@ -264,7 +304,8 @@ rg_wrap_kernel(const T* __restrict__ pos, int64_t N, Geom<T> g, int vec_ok, Vec4
 template <typename T>
 __global__ void __launch_bounds__(256)
 rg_grid_kernel(DevHeader* h, double radius, long long src_capacity, long long cell_capacity, int cand_capacity,
-               int force_sx, int force_sy, const unsigned long long* __restrict__ partials, int num_partials)
+               int force_sx, int force_sy, const unsigned long long* __restrict__ partials, int num_partials,
+               const unsigned long long* __restrict__ tpartials, int num_tpartials)
 {
     {   // reduce the per-block partials of rg_wrap_kernel into the header
         __shared__ unsigned long long red[7][8];
@@ -298,8 +339,38 @@ rg_grid_kernel(DevHeader* h, double radius, long long src_capacity, long long ce
             }
         }
     }
+    __shared__ unsigned long long tbox[6];
+    {   // bounding box of the target subset (if any), same block reduction
+        __shared__ unsigned long long tred[6][8];
+        unsigned long long v[6] = {~0ull, ~0ull, ~0ull, 0ull, 0ull, 0ull};
+        for (int b = threadIdx.x; b < num_tpartials; b += blockDim.x) {
+#pragma unroll
+            for (int k = 0; k < 3; k++) {
+                v[k] = min(v[k], tpartials[(size_t)b * 8 + k]);
+                v[3 + k] = max(v[3 + k], tpartials[(size_t)b * 8 + 3 + k]);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int k = 0; k < 3; k++) {
+                v[k] = min(v[k], __shfl_xor_sync(0xffffffffu, v[k], o));
+                v[3 + k] = max(v[3 + k], __shfl_xor_sync(0xffffffffu, v[3 + k], o));
+            }
+        if ((threadIdx.x & 31) == 0)
+            for (int k = 0; k < 6; k++) tred[k][threadIdx.x >> 5] = v[k];
+        __syncthreads();
+        if (threadIdx.x < 6) {
+            unsigned long long a = tred[threadIdx.x][0];
+            for (int w = 1; w < (int)(blockDim.x >> 5); w++)
+                a = (threadIdx.x < 3) ? min(a, tred[threadIdx.x][w]) : max(a, tred[threadIdx.x][w]);
+            tbox[threadIdx.x] = a;
+        }
+        __syncthreads();
+    }
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     if (h->M > (unsigned long long)src_capacity) h->status |= DYNB_RG_SRC_OVERFLOW;
+    for (int k = 0; k < 3; k++) { h->clip_lo[k] = -1.0e300; h->clip_hi[k] = 1.0e300; }
     if (h->M == 0 || (h->status & RG_FATAL)) {
         h->nx = h->ny = h->nz = 1;
         h->ncell_plus1 = 2;
@@ -315,7 +386,18 @@ rg_grid_kernel(DevHeader* h, double radius, long long src_capacity, long long ce
     double lo[3], ext[3];
     for (int k = 0; k < 3; k++) {
         lo[k] = unordered_any<T>(h->bb_min[k]) - 0.01;
-        ext[k] = unordered_any<T>(h->bb_max[k]) + 0.01 - lo[k];
+        double hi = unordered_any<T>(h->bb_max[k]) + 0.01;
+        if (num_tpartials > 0 && tbox[k] <= tbox[3 + k]) {
+            // clip to the targets' box grown by the cutoff (with slack far above any rounding)
+            const double margin = radius * 1.001 + 0.02;
+            const double tlo = unordered_any<T>(tbox[k]) - margin, thi = unordered_any<T>(tbox[3 + k]) + margin;
+            if (tlo > lo[k]) lo[k] = tlo;
+            if (thi < hi) hi = thi;
+            h->clip_lo[k] = lo[k];
+            h->clip_hi[k] = hi;
+            if (hi < lo[k]) hi = lo[k];
+        }
+        ext[k] = hi - lo[k];
     }
     double res = radius / 1.99;
     long long n[3];
@@ -391,6 +473,9 @@ rg_bin_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ targets, Geom<T
                     if (!image_needed(flags, dx, dy, dz)) continue;
                     T x, y, z;
                     image_pos(g, w.x, w.y, w.z, dx, dy, dz, x, y, z);
+                    if ((double)x < h.clip_lo[0] || (double)x > h.clip_hi[0] || (double)y < h.clip_lo[1] || (double)y > h.clip_hi[1] ||
+                        (double)z < h.clip_lo[2] || (double)z > h.clip_hi[2])
+                        continue;  // farther than the cutoff from every target
                     const uint32_t c = cell_of(h, x, y, z);
                     if (!SCATTER) {
                         atomicAdd(&ccount[c], 1u);
@@ -772,7 +857,7 @@ __global__ void rg_zero_counts_kernel(int64_t Nt, int32_t* counts_out)
 // host side
 // ------------------------------------------------------------------------------------------
 struct RgLayout {
-    int64_t hdr, partials, posw, aff, ccount, cfill, tccount, tcfill, skey, scell, spos, scode, tkey, tcell, tpos, tmeta,
+    int64_t hdr, partials, tpartials, posw, aff, ccount, cfill, tccount, tcfill, skey, scell, spos, scode, tkey, tcell, tpos, tmeta,
         tcount, toffset, sums, total;
 };
 
@@ -789,6 +874,7 @@ static RgLayout rg_layout(int64_t N, int64_t Nt, int64_t src_cap, int64_t cell_c
     L.tccount = take((cell_cap + 2) * 4);
     L.tcfill = take((cell_cap + 2) * 4);
     L.partials = take(((N + 255) / 256 + 1) * 64);
+    L.tpartials = take(((Nt + 255) / 256 + 1) * 64);
     L.posw = take(N * v4);
     L.aff = take(N * 16);
     L.skey = take(src_cap * 8);
@@ -955,15 +1041,23 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
     if (const char* env = getenv("DYNB_RG_GROUP")) sscanf(env, "%d,%d", &force_sx, &force_sy);
     if (force_sx < 0 || force_sx > 8) force_sx = 0;
     if (force_sy < 0 || force_sy > 2) force_sy = 0;
+    int n_tpart = 0;
+    if (targets != nullptr) {
+        n_tpart = (int)((Nt + 255) / 256);
+        rg_target_bbox_kernel<T><<<n_tpart, 256, 0, stream>>>(targets, Nt, N, posw, reinterpret_cast<unsigned long long*>(w + L.tpartials));
+    }
     rg_grid_kernel<T><<<1, 256, 0, stream>>>(h, radius, (long long)src_cap, (long long)cell_cap,
                                              PAIR_CAND_BYTES / (int)sizeof(Vec4<T>), force_sx, force_sy,
                                              reinterpret_cast<const unsigned long long*>(w + L.partials),
-                                             (int)((N + WRAP_THREADS - 1) / WRAP_THREADS));
+                                             (int)((N + WRAP_THREADS - 1) / WRAP_THREADS),
+                                             reinterpret_cast<const unsigned long long*>(w + L.tpartials), n_tpart);
 
     const int64_t nb = std::max(N, Nt);
     rg_bin_kernel<T, false><<<(unsigned)((nb + 255) / 256), 256, 0, stream>>>(
         N, Nt, targets, g, posw, h, ccount, cfill, tccount, tcfill, skey, scell, tkey, tcell);
-    DYNB_CUDA_OK((exclusive_scan<uint32_t, uint32_t>(ccount, ccount, &h->ncell_plus1, cell_cap + 1, sums32, nullptr, stream)));
+    // the scan total is the number of source images actually binned (<= the count of rg_wrap when clipping): it becomes header.M
+    DYNB_CUDA_OK((exclusive_scan<uint32_t, uint32_t>(ccount, ccount, &h->ncell_plus1, cell_cap + 1, sums32,
+                                                      reinterpret_cast<uint32_t*>(&h->M), stream)));
     DYNB_CUDA_OK((exclusive_scan<uint32_t, uint32_t>(tccount, tccount, &h->ncell_plus1, cell_cap + 1, sums32, nullptr, stream)));
     rg_bin_kernel<T, true><<<(unsigned)((nb + 255) / 256), 256, 0, stream>>>(
         N, Nt, targets, g, posw, h, ccount, cfill, tccount, tcfill, skey, scell, tkey, tcell);

@@ -267,5 +267,5 @@ def radius_graph_pbc_cuda(data, radius: float, max_num_neighbors_threshold: int,
 def launches_per_graph() -> int:
     """Kernels one radius_graph_pbc call launches: zero-degrees, wrap, grid, cell histogram,
     2 x 3 scan kernels (source and target cells), scatter, finalize, count pass, degree post-pass,
-    3 scan kernels (edge offsets), edge-writing pass."""
+    3 scan kernels (edge offsets), edge-writing pass (one more, the target bounding box, with a target subset)."""
     return 18
