@@ -274,7 +274,7 @@ def run_ours(args):
     alg_bytes = 28.0 * plan.E
     achieved = alg_bytes / (fill_ms * 1e-3) / 1e9
     traffic = None
-    tp = os.path.join(ROOT, "profiles", "rg_pair_fill_traffic.json")
+    tp = os.path.join(ROOT, "profiles", "rg_pair_fill_traffic.txt")
     if os.path.exists(tp):
         with open(tp) as f:
             tj = json.load(f)
