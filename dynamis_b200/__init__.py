@@ -32,6 +32,7 @@ from .partition import (  # noqa: F401
     sfc_keys,
     sfc_partition_labels,
 )
+from .sim_state import DRIFT_BREACH, DRIFT_TRIP, SimState, scatter_rows  # noqa: F401
 from .state import (  # noqa: F401
     DistEnvironment,
     DynamisState,

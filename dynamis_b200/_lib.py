@@ -78,6 +78,8 @@ SIGNATURES = {
     "dynb_ipc_close": (_i32, [_p]),
     "dynb_enable_peer_access": (_i32, [_i32]),
     "dynb_copy_async": (_i32, [_p, _p, _i64, _p]),
+    "dynb_scatter_rows": (_i32, [_p, _i64, _p, _i64, _i64, _p, _p, _p]),
+    "dynb_drift_flag": (_i32, [_p, _p, _p, _p, _i64, _f64, _f64, _p, _p, _p]),
     "dynb_sfc_static_max_atoms": (_i64, []),
     "dynb_sfc_partition_static": (_i32, [_p, _i64, _p, _i64, _i32, _p, _p, _p]),
 }

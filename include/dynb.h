@@ -221,6 +221,19 @@ int dynb_enable_peer_access(int peer_device);
 /* Device-to-device copy on the stream (the local rows and ghost rows of the concatenated result). */
 int dynb_copy_async(void* dst_dev, const void* src_dev, int64_t bytes, void* stream);
 
+/* ------------------------------------------------------------------ repartition / drift watchdog
+ * out[idx[i], :] = rows[i, :] for unique idx: puts rows gathered from all ranks back into canonical
+ * atom order (replaces cat + argsort + gather, dynamis/src/dynamis/simulatorState.py:172-183, and the
+ * per-rank index_put loop of :238-242).  bad_dev (optional) is set when an index is outside [0, n_out). */
+int dynb_scatter_rows(const void* rows_dev, int64_t row_bytes, const int64_t* idx_dev, int64_t n, int64_t n_out,
+                      void* out_dev, uint32_t* bad_dev, void* stream);
+/* The 2-bit drift word of SimState.write_local_drift_flag (simulatorState.py:257-293) in one kernel:
+ * bit 0 when max_i(|x_i - ref_i| + dt (|v_i| + |v_i - vprev_i|)) >= threshold, bit 1 when
+ * max_i |x_i - ref_i| > threshold; prev_vel_dev is overwritten with vel_dev.  state_dev: 3 zero-initialised
+ * uint32 words owned by the caller (left zero again by every call). */
+int dynb_drift_flag(const float* cur_dev, const float* ref_dev, const float* vel_dev, float* prev_vel_dev, int64_t n,
+                    double dt, double threshold, uint32_t* state_dev, int32_t* flag_dev, void* stream);
+
 /* ------------------------------------------------------------------ partition without a workspace
  * No counterpart in the reference.  Same result as dynb_sfc_partition, for callers that must not
  * allocate device memory while they run (an engine that gave its whole memory budget to its own

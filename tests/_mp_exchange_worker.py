@@ -90,6 +90,45 @@ def main():
         sel = pid_b[gfull["dst"]] == rank
         want = O.canonical_edges(gfull["src"][sel], gfull["dst"][sel], gfull["shift"][sel])
         assert mine.shape == want.shape and (mine == want).all(), f"DistGraphBuilder edges differ (pass {it})"
+    # SimState across real ranks: atoms drift, the state is gathered, repartitioned and rebuilt
+    mol = D.MolecularInfo()
+    mol.num_atoms = n
+    mol.atom_positions = torch.as_tensor(pos, device=dev)
+    vel_np = np.random.default_rng(7).normal(0, 0.05, (n, 3)).astype(np.float32)
+    mol.atom_velocities = torch.as_tensor(vel_np, device=dev)
+    mol.atom_types = torch.zeros(n, dtype=torch.int64, device=dev)
+    mol.atom_vertex_numbers = torch.arange(n, dtype=torch.int64, device=dev)
+    cfg2 = D.SimulationConfig()
+    cfg2.cutoff, cfg2.ghost_cutoff_buffer, cfg2.cell, cfg2.pbc = 6.0, 0.5, torch.as_tensor(cell), torch.tensor([True] * 3)
+    env.local_rank = dev.index
+    sim = D.SimState(mol, D.SFCPartitioner(), cfg2, env, device=dev)
+    old_idx = sim.local_partition_info.partition_indices.clone()
+    for _ in range(3):
+        sim.pos.add_(sim.vel)                      # x += v, three steps
+    want_pos = pos + 3 * vel_np
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    sim.write_local_drift_flag(flag, 0.25, 1.0)
+    d = np.linalg.norm(3 * vel_np[old_idx.cpu().numpy()], axis=1)
+    assert int(flag.item()) & 2 == (2 if d.max() > 0.25 else 0)
+    sim.sync_positions_and_rebuild_halo()
+    np.testing.assert_allclose(sim._state.global_molecular_info.atom_positions.cpu().numpy(), want_pos, rtol=0, atol=1e-5)
+    g2 = O.radius_graph(want_pos.astype(np.float32), cell, [1, 1, 1], np.float32(6.5))
+    m2 = O.build_halo_maps(g2["src"], g2["dst"], pid, rank, W)
+    gp = sim._state.global_molecular_info.atom_positions.cpu().numpy()
+    if np.array_equal(gp, want_pos.astype(np.float32)):
+        assert np.array_equal(sim.local_partition_info.send_local_indices.cpu().numpy(), m2["send_local_indices"])
+    sim.sync_and_repartition()
+    gp = sim._state.global_molecular_info.atom_positions.cpu().numpy()
+    gv = sim._state.global_molecular_info.atom_velocities.cpu().numpy()
+    assert np.array_equal(gv, vel_np)
+    pid3 = O.sfc_partition(gp, None, W, 0)
+    assert np.array_equal(sim.local_partition_info.partition_id.cpu().numpy(), pid3)
+    mine3 = np.nonzero(pid3 == rank)[0]
+    assert np.array_equal(sim.local_partition_info.partition_indices.cpu().numpy(), mine3)
+    assert np.array_equal(sim.pos.cpu().numpy(), gp[mine3]) and np.array_equal(sim.vel.cpu().numpy(), vel_np[mine3])
+    g3 = O.radius_graph(gp, cell, [1, 1, 1], np.float32(6.5))
+    m3 = O.build_halo_maps(g3["src"], g3["dst"], pid3, rank, W)
+    assert np.array_equal(sim.local_partition_info.recv_atom_global.cpu().numpy(), m3["recv_atom_global"])
     dist.barrier()
     dist.destroy_process_group()
     print(f"rank {rank}: ok", flush=True)
