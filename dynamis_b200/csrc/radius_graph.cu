@@ -574,7 +574,7 @@ constexpr int PAIR_WARPS = 8;
 constexpr int PAIR_THREADS = PAIR_WARPS * 32;
 constexpr int PAIR_CAND_BYTES = 5120;  // dense candidate records per warp (320 float4 / 160 double4)
 constexpr int PAIR_CODE_BYTES = 1280;  // packed shift code per candidate (up to 320)
-constexpr int PAIR_LIST = 128;         // parked hits per warp (uint32 each)
+constexpr int PAIR_LIST = 128;         // parked hits per target (uint16 each, two targets per warp)
 constexpr int PAIR_WARP_BYTES = PAIR_CAND_BYTES + PAIR_CODE_BYTES + PAIR_LIST * 4;
 
 enum { MODE_COUNT = 0, MODE_FILL = 1, MODE_HALO = 2 };
@@ -619,7 +619,8 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
     unsigned char* wbase = smem_raw + warp * PAIR_WARP_BYTES;
     Vec4<T>* cand = reinterpret_cast<Vec4<T>*>(wbase);
     uint32_t* codes = reinterpret_cast<uint32_t*>(wbase + PAIR_CAND_BYTES);
-    uint32_t* list = reinterpret_cast<uint32_t*>(wbase + PAIR_CAND_BYTES + PAIR_CODE_BYTES);
+    unsigned short* listA = reinterpret_cast<unsigned short*>(wbase + PAIR_CAND_BYTES + PAIR_CODE_BYTES);
+    unsigned short* listB = listA + PAIR_LIST;
 
     const DevHeader* hp = p.h;
     if (hp->status & RG_FATAL) return;
@@ -740,7 +741,7 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                         ownA = halo.owner[tmA.x];
                         ownB = halo.owner[tmB.x];
                     }
-                    int n = 0;  // parked entries
+                    int n = 0, nB = 0;  // parked hits of target A / target B
                     for (int k = 0; k < clen32; k += 32) {
                         const int j = k + lane;
                         const Vec4<T> c = cand[j];
@@ -767,37 +768,43 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                                 }
                             }
                         } else {
+                            // each target parks the slots of its hits in its own half of the list; the index in
+                            // the half is the position inside the target's edge run since the last write-out
                             const uint32_t mA = __ballot_sync(0xffffffffu, hitA);
                             const uint32_t mB = __ballot_sync(0xffffffffu, hitB);
-                            const int nA = __popc(mA);
-                            // entry: candidate slot (10 bits) | target select (1 bit) | position inside the target's edge run
-                            if (hitA) list[n + __popc(mA & lt)] = (uint32_t)j | ((uint32_t)(prodA + __popc(mA & lt)) << 11);
-                            if (hitB) list[n + nA + __popc(mB & lt)] = (uint32_t)j | (1u << 10) | ((uint32_t)(prodB + __popc(mB & lt)) << 11);
-                            prodA += nA;
-                            prodB += __popc(mB);
-                            n += nA + __popc(mB);
-                            if (n > PAIR_LIST - 64 || k + 32 >= clen32) {
+                            if (hitA) listA[n + __popc(mA & lt)] = (unsigned short)j;
+                            if (hitB) listB[nB + __popc(mB & lt)] = (unsigned short)j;
+                            n += __popc(mA);
+                            nB += __popc(mB);
+                            if (n > PAIR_LIST - 32 || nB > PAIR_LIST - 32 || k + 32 >= clen32) {
                                 __syncwarp();
-                                for (int i = lane; i < n; i += 32) {
-                                    const uint32_t ent = list[i];
-                                    const int jh = (int)(ent & 1023u);
-                                    const bool selB = (ent >> 10) & 1u;
-                                    const Vec4<T> ch = cand[jh];
-                                    const uint32_t code = codes[jh];
-                                    const int4 tm = selB ? tmB : tmA;
-                                    const long long e = (selB ? baseB : baseA) + (long long)(ent >> 11);
-                                    ei[e] = (long long)real_to_bits(ch.w);
-                                    ei[E + e] = (long long)tm.x;
-                                    shifts[3 * e + 0] = (float)((int)(code & 1023u) - 512 + tm.y);
-                                    shifts[3 * e + 1] = (float)((int)((code >> 10) & 1023u) - 512 + tm.z);
-                                    shifts[3 * e + 2] = (float)((int)((code >> 20) & 1023u) - 512 + tm.w);
-                                    if (d2out != nullptr) {
-                                        const T tx = selB ? bx : ax, ty = selB ? by : ay, tz = selB ? bz : az;
-                                        const T hx = ch.x, hy = ch.y, hz = ch.z;
-                                        d2out[e] = (tx - hx) * (tx - hx) + (ty - hy) * (ty - hy) + (tz - hz) * (tz - hz);
+#pragma unroll
+                                for (int sel = 0; sel < 2; sel++) {
+                                    const int cntX = sel ? nB : n;
+                                    const unsigned short* lx = sel ? listB : listA;
+                                    const int4 tm = sel ? tmB : tmA;
+                                    const long long bX = (sel ? baseB + prodB : baseA + prodA);
+                                    for (int i = lane; i < cntX; i += 32) {
+                                        const int jh = lx[i];
+                                        const Vec4<T> ch = cand[jh];
+                                        const uint32_t code = codes[jh];
+                                        const long long e = bX + i;
+                                        ei[e] = (long long)real_to_bits(ch.w);
+                                        ei[E + e] = (long long)tm.x;
+                                        shifts[3 * e + 0] = (float)((int)(code & 1023u) - 512 + tm.y);
+                                        shifts[3 * e + 1] = (float)((int)((code >> 10) & 1023u) - 512 + tm.z);
+                                        shifts[3 * e + 2] = (float)((int)((code >> 20) & 1023u) - 512 + tm.w);
+                                        if (d2out != nullptr) {
+                                            const T tx = sel ? bx : ax, ty = sel ? by : ay, tz = sel ? bz : az;
+                                            const T hx = ch.x, hy = ch.y, hz = ch.z;
+                                            d2out[e] = (tx - hx) * (tx - hx) + (ty - hy) * (ty - hy) + (tz - hz) * (tz - hz);
+                                        }
                                     }
                                 }
+                                prodA += n;
+                                prodB += nB;
                                 n = 0;
+                                nB = 0;
                                 __syncwarp();
                             }
                         }
