@@ -5,8 +5,9 @@
 //
 // Pipeline (one stream, no host synchronisation inside the plan):
 //   rg_wrap        wrap positions into the unit cell, classify which periodic images each atom
-//                  needs, reduce the bounding box of all images          (ref :596-605, :18-67)
-//   rg_grid        one thread: choose the cell grid on the device        (ref :662-692)
+//                  needs, per-block bounding box of all images           (ref :596-605, :18-67)
+//   rg_target_bbox bounding box of the targets (only with a target subset)
+//   rg_grid        one block: reduce the boxes, choose the cell grid on the device (ref :662-692)
 //   rg_bin_count   histogram of images / targets per cell (atomics)      (ref :146-171)
 //   scan           cell starts
 //   rg_bin_scatter provisional slot inside each cell (atomic rank)
@@ -20,12 +21,13 @@
 // the periodic-image test with the image position, and d2 <= r2 && d2 > 1e-8f.  The cell grid
 // only decides which pairs are examined and is free to differ.
 //
-// Work decomposition of rg_pair: one warp owns a run of `group_cells` consecutive cells along x
-// and all targets inside.  It copies the (2*pad+1)^2 contiguous runs of neighbouring source
-// records into a dense shared-memory list once, then every target is tested against the dense
-// list with one candidate per lane (conflict-free 16-byte shared loads, ballot + popc
-// compaction).  Hits are parked in a small per-warp list and written out 32 edges at a time so
-// that the 8-byte index stores of a warp cover one contiguous 256-byte run.
+// Work decomposition of rg_pair: one warp owns a group of group_cells x group_cells_y cells (x, y)
+// and all targets inside.  It flattens the contiguous runs of neighbouring source records (one run
+// per (y, z) row, one lane per run) into a dense shared-memory list once, then tests the targets two
+// at a time against the list with one candidate per lane (conflict-free 16-byte shared loads, ballot +
+// popc compaction).  Hits are parked in per-target lists and written out 32 edges at a time so that
+// the 8-byte index stores of a warp cover one contiguous 256-byte run.  With a target subset the
+// source images are first clipped to the targets' bounding box grown by the cutoff.
 
 #include "common.cuh"
 #include "scan.cuh"
