@@ -521,7 +521,7 @@ rg_bin_finalize_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ target
                        const uint32_t* __restrict__ tcstart, const unsigned long long* __restrict__ skey,
                        const uint32_t* __restrict__ scell, const uint32_t* __restrict__ tkey,
                        const uint32_t* __restrict__ tcell, Vec4<T>* __restrict__ spos,
-                       uint32_t* __restrict__ scode, Vec4<T>* __restrict__ tpos, int4* __restrict__ tmeta)
+                       uint32_t* __restrict__ scode, uint2* __restrict__ smeta, Vec4<T>* __restrict__ tpos, int4* __restrict__ tmeta)
 {
     const DevHeader h = *hp;
     if (h.status & RG_FATAL) return;
@@ -549,8 +549,10 @@ rg_bin_finalize_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ target
         if (ex < -511 || ex > 511 || ey < -511 || ey > 511 || ez < -511 || ez > 511) {
             atomicOr(&hp->status, DYNB_RG_SHIFT_RANGE);
             scode[b + rank] = pack_shift_code(0, 0, 0);
+            smeta[b + rank] = make_uint2((uint32_t)atom, pack_shift_code(0, 0, 0));
         } else {
             scode[b + rank] = pack_shift_code(ex, ey, ez);
+            smeta[b + rank] = make_uint2((uint32_t)atom, pack_shift_code(ex, ey, ez));
         }
     }
     if (j < Nt) {
@@ -592,8 +594,10 @@ struct HaloArgs {
     int words;
 };
 
+constexpr int RG_MASK_SLOTS = 16;  // hit bits kept per lane and target (candidate lists up to 512 records)
+
 template <typename T> struct PairParams {
-    const DevHeader* h;
+    DevHeader* h;
     const uint32_t* cstart;
     const uint32_t* tcstart;
     const Vec4<T>* spos;
@@ -602,6 +606,8 @@ template <typename T> struct PairParams {
     const int4* tmeta;
     uint32_t* tcount;         // [Nt+1] degree per sorted target; running cursor in FILL
     const long long* toffset; // [Nt+1]
+    unsigned short* hitmask;  // [Nt, 32] per lane: bit s set if candidate 32 s + lane is a neighbour (written by COUNT)
+    const uint2* smeta;       // [M] {atom id, packed shift code} per source record
     T r2;
 };
 // The plan stores its PairParams inside the workspace (after the header) so that the fill call
@@ -612,7 +618,7 @@ constexpr int64_t RG_HEADER_BYTES = 1024;
 template <typename T, int MODE>
 __global__ void __launch_bounds__(PAIR_THREADS, 4)
 rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restrict__ ei, float* __restrict__ shifts,
-               T* __restrict__ d2out, const long long E, const HaloArgs halo)
+               T* __restrict__ d2out, const long long E, const HaloArgs halo, const int skip_if_masks)
 {
     const PairParams<T> p = *params_dev;
     extern __shared__ __align__(32) unsigned char smem_raw[];
@@ -624,8 +630,10 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
     unsigned short* listA = reinterpret_cast<unsigned short*>(wbase + PAIR_CAND_BYTES + PAIR_CODE_BYTES);
     unsigned short* listB = listA + PAIR_LIST;
 
-    const DevHeader* hp = p.h;
+    DevHeader* hp = p.h;
     if (hp->status & RG_FATAL) return;
+    if (MODE == MODE_FILL && skip_if_masks && hp->reserved[0] <= RG_MASK_SLOTS) return;  // rg_fillmask_kernel does it
+    int warp_max_slots = 0;
     const int nx = hp->nx, ny = hp->ny, nz = hp->nz, S = hp->group_cells, Sy = hp->group_cells_y, pad = hp->pad;
     const uint32_t gx = (uint32_t)hp->gx;
     const uint32_t gy = (uint32_t)((ny + Sy - 1) / Sy);
@@ -669,6 +677,9 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
         }
         int L;
         const int run_off = warp_excl_scan(run_len, lane, &L);
+        const int nslots_total = (L + 31) >> 5;
+        const bool write_masks = (MODE == MODE_COUNT) && nslots_total <= RG_MASK_SLOTS;
+        warp_max_slots = max(warp_max_slots, nslots_total);
 
         for (int cbeg = 0, chunk = 0; cbeg < L; cbeg += CAP, chunk++) {
             const int clen = min(CAP, L - cbeg);
@@ -714,7 +725,36 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                     prodA = (int)p.tcount[t];
                     prodB = has2 ? (int)p.tcount[t + 1] : 0;
                 }
-                if (MODE == MODE_COUNT) {
+                if (MODE == MODE_COUNT && write_masks) {
+                    // lane l keeps, for each of its candidates l, 32 + l, 64 + l, ..., one hit bit per target;
+                    // the bits are stored so that the edge-writing pass need not repeat the distance tests
+                    unsigned short* mrowA = p.hitmask + (size_t)t * 32;
+                    unsigned short* mrowB = p.hitmask + (size_t)(has2 ? t + 1 : t) * 32;
+                    uint32_t bitsA = 0, bitsB = 0;
+                    if (chunk != 0) {
+                        bitsA = mrowA[lane];
+                        bitsB = mrowB[lane];
+                    }
+                    uint32_t bit = 1u << (cbeg >> 5);
+#pragma unroll 2
+                    for (int k = 0; k < clen32; k += 32) {
+                        const Vec4<T> c = cand[k + lane];
+                        const T sx = c.x, sy = c.y, sz = c.z;
+                        const T dA = (ax - sx) * (ax - sx) + (ay - sy) * (ay - sy) + (az - sz) * (az - sz);
+                        const T dB = (bx - sx) * (bx - sx) + (by - sy) * (by - sy) + (bz - sz) * (bz - sz);
+                        bitsA |= ((dA <= r2) && (dA > eps)) ? bit : 0u;
+                        bitsB |= ((dB <= r2) && (dB > eps)) ? bit : 0u;
+                        bit <<= 1;
+                    }
+                    mrowA[lane] = (unsigned short)bitsA;
+                    if (has2) mrowB[lane] = (unsigned short)bitsB;
+                    const int ca = __reduce_add_sync(0xffffffffu, __popc(bitsA));
+                    const int cb = __reduce_add_sync(0xffffffffu, __popc(bitsB));
+                    if (lane == 0) {
+                        p.tcount[t] = (uint32_t)ca;
+                        if (has2) p.tcount[t + 1] = (uint32_t)cb;
+                    }
+                } else if (MODE == MODE_COUNT) {
                     int ca = 0, cb = 0;
 #pragma unroll 2
                     for (int k = 0; k < clen32; k += 32) {
@@ -830,6 +870,133 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                 for (uint32_t t = tb[yr] + lane; t < te[yr]; t += 32) p.tcount[t] = 0;
         }
     }
+    // longest candidate list of any group with targets, in 32-record slots (one atomic per warp)
+    if (MODE == MODE_COUNT && lane == 0 && warp_max_slots > 0) atomicMax(&hp->reserved[0], (long long)warp_max_slots);
+}
+
+// ------------------------------------------------------------------------------------------
+// Edge writer driven by the hit masks of the counting pass.  When no group's candidate list is longer
+// than RG_MASK_SLOTS * 32 records (the usual case: about 27 cells of 8-16 atoms) and the caller does
+// not ask for distances, the edges follow from the masks alone: a warp stages {atom id, shift code}
+// of its group's candidates, reads each target's mask words and writes the edge run.  No position is
+// loaded and no distance is recomputed, and the edge order is the one rg_pair_kernel<FILL> gives.
+// ------------------------------------------------------------------------------------------
+constexpr int FM_META = RG_MASK_SLOTS * 32;                       // staged candidate records per warp
+constexpr int FM_WARP_BYTES = FM_META * 8 + FM_META * 2;    // records + one parked slot per possible hit
+
+template <typename T>
+__global__ void __launch_bounds__(PAIR_THREADS, 4)
+rg_fillmask_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restrict__ ei, float* __restrict__ shifts,
+                   const long long E)
+{
+    const PairParams<T> p = *params_dev;
+    extern __shared__ __align__(32) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned char* wbase = smem_raw + warp * FM_WARP_BYTES;
+    uint2* meta = reinterpret_cast<uint2*>(wbase);
+    unsigned short* list = reinterpret_cast<unsigned short*>(wbase + FM_META * 8);
+
+    const DevHeader* hp = p.h;
+    if (hp->status & RG_FATAL) return;
+    if (hp->reserved[0] > RG_MASK_SLOTS) return;  // masks incomplete: rg_pair_kernel<FILL> writes the edges
+    const int nx = hp->nx, ny = hp->ny, nz = hp->nz, S = hp->group_cells, Sy = hp->group_cells_y, pad = hp->pad;
+    const uint32_t gx = (uint32_t)hp->gx;
+    const uint32_t gy = (uint32_t)((ny + Sy - 1) / Sy);
+    const uint32_t num_groups = (uint32_t)hp->num_groups;
+    const int Wd = 2 * pad + 1, Wy = Sy + 2 * pad, nrun = Wy * Wd;
+    const int lane_dy = (lane % Wy) - pad, lane_dz = (lane / Wy) - pad;
+    const uint32_t lt = lanemask_lt();
+
+    const uint32_t nwarps = gridDim.x * PAIR_WARPS;
+    for (uint32_t grp = blockIdx.x * PAIR_WARPS + warp; grp < num_groups; grp += nwarps) {
+        const uint32_t row = grp / gx;
+        const int ix = (int)(grp - row * gx);
+        const int cz = (int)(row / gy), iy = (int)(row - (uint32_t)cz * gy);
+        const int cx0 = ix * S, cx1 = min(cx0 + S, nx) - 1;
+        const int cy0 = iy * Sy, cy1 = min(cy0 + Sy, ny) - 1;
+        uint32_t tb[2], te[2];
+        tb[0] = p.tcstart[((uint32_t)cz * ny + cy0) * nx + cx0];
+        te[0] = p.tcstart[((uint32_t)cz * ny + cy0) * nx + cx1 + 1];
+        tb[1] = te[1] = 0;
+        if (cy1 > cy0) {
+            tb[1] = p.tcstart[((uint32_t)cz * ny + cy1) * nx + cx0];
+            te[1] = p.tcstart[((uint32_t)cz * ny + cy1) * nx + cx1 + 1];
+        }
+        if (tb[0] == te[0] && tb[1] == te[1]) continue;
+
+        int run_a = 0, run_len = 0;
+        if (lane < nrun) {
+            const int yy = cy0 + lane_dy, zz = cz + lane_dz;
+            if (yy >= 0 && yy < ny && yy <= cy1 + pad && zz >= 0 && zz < nz) {
+                const uint32_t b = ((uint32_t)zz * ny + yy) * nx;
+                const uint32_t a = p.cstart[b + max(cx0 - pad, 0)];
+                const uint32_t e = p.cstart[b + min(cx1 + pad, nx - 1) + 1];
+                run_a = (int)a;
+                run_len = (int)(e - a);
+            }
+        }
+        int L;
+        const int run_off = warp_excl_scan(run_len, lane, &L);
+        const int nslots = min((L + 31) >> 5, RG_MASK_SLOTS);
+        if (nslots == 0) continue;
+
+        __syncwarp();
+        for (int j = lane; j < nslots * 32; j += 32) {
+            int r = 0;
+#pragma unroll
+            for (int step = 16; step >= 1; step >>= 1) {
+                const int cr = r + step;
+                const int o = __shfl_sync(0xffffffffu, run_off, cr & 31);
+                if (cr < 32 && o <= j) r = cr;
+            }
+            const int gidx = __shfl_sync(0xffffffffu, run_a, r) + (j - __shfl_sync(0xffffffffu, run_off, r));
+            if (j < L) meta[j] = p.smeta[gidx];
+        }
+        __syncwarp();
+
+        // Targets of both rows as one list, one at a time; the words of the next target are requested
+        // before the current one is written.  Lane l holds the hit bits of candidates l, 32 + l, ...:
+        // a warp scan of the bit counts gives every lane the place of its first edge, so the edges of a
+        // target are ordered by (candidate mod 32, candidate / 32).
+        const int n0 = (int)(te[0] - tb[0]), nT = n0 + (int)(te[1] - tb[1]);
+        int4 ntm;
+        long long nbase;
+        uint32_t nw;
+        {
+            const uint32_t t = n0 > 0 ? tb[0] : tb[1];
+            ntm = p.tmeta[t]; nbase = p.toffset[t]; nw = p.hitmask[(size_t)t * 32 + lane];
+        }
+        for (int q = 0; q < nT; q++) {
+            const int4 tm = ntm;
+            const long long base = nbase;
+            uint32_t w = nw;
+            if (q + 1 < nT) {
+                const int qa = q + 1;
+                const uint32_t t = qa < n0 ? tb[0] + qa : tb[1] + (qa - n0);
+                ntm = p.tmeta[t]; nbase = p.toffset[t]; nw = p.hitmask[(size_t)t * 32 + lane];
+            }
+            int cnt;
+            int pos = warp_excl_scan(__popc(w), lane, &cnt);
+            __syncwarp();
+            while (w) {
+                const int sbit = __ffs((int)w) - 1;
+                w &= w - 1;
+                list[pos++] = (unsigned short)(sbit * 32 + lane);
+            }
+            __syncwarp();
+            const int sx = tm.y - 512, sy = tm.z - 512, sz = tm.w - 512;
+            for (int i = lane; i < cnt; i += 32) {
+                const uint2 m = meta[list[i]];
+                const uint32_t code = m.y;
+                const long long e = base + i;
+                ei[e] = (long long)m.x;
+                ei[E + e] = (long long)tm.x;
+                shifts[3 * e + 0] = (float)((int)(code & 1023u) + sx);
+                shifts[3 * e + 1] = (float)((int)((code >> 10) & 1023u) + sy);
+                shifts[3 * e + 2] = (float)((int)((code >> 20) & 1023u) + sz);
+            }
+        }
+    }
 }
 
 // degree in caller order + maximum degree
@@ -866,7 +1033,7 @@ __global__ void rg_zero_counts_kernel(int64_t Nt, int32_t* counts_out)
 // host side
 // ------------------------------------------------------------------------------------------
 struct RgLayout {
-    int64_t hdr, partials, tpartials, posw, aff, ccount, cfill, tccount, tcfill, skey, scell, spos, scode, tkey, tcell, tpos, tmeta,
+    int64_t hdr, partials, tpartials, posw, aff, ccount, cfill, tccount, tcfill, skey, scell, spos, scode, smeta, hitmask, tkey, tcell, tpos, tmeta,
         tcount, toffset, sums, total;
 };
 
@@ -890,6 +1057,8 @@ static RgLayout rg_layout(int64_t N, int64_t Nt, int64_t src_cap, int64_t cell_c
     L.scell = take(src_cap * 4);
     L.spos = take(src_cap * v4);
     L.scode = take(src_cap * 4);
+    L.smeta = take(src_cap * 8);
+    L.hitmask = take(Nt * 32 * 2);
     L.tkey = take(Nt * 4);
     L.tcell = take(Nt * 4);
     L.tpos = take(Nt * v4);
@@ -1011,6 +1180,8 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
     auto* scell = reinterpret_cast<uint32_t*>(w + L.scell);
     auto* spos = reinterpret_cast<Vec4<T>*>(w + L.spos);
     auto* scode = reinterpret_cast<uint32_t*>(w + L.scode);
+    auto* smeta = reinterpret_cast<uint2*>(w + L.smeta);
+    auto* hitmask = reinterpret_cast<unsigned short*>(w + L.hitmask);
     auto* tkey = reinterpret_cast<uint32_t*>(w + L.tkey);
     auto* tcell = reinterpret_cast<uint32_t*>(w + L.tcell);
     auto* tpos = reinterpret_cast<Vec4<T>*>(w + L.tpos);
@@ -1031,7 +1202,7 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
         for (int k = 0; k < 3; k++) { hi.bb_min[k] = ~0ull; hi.bb_max[k] = 0ull; }
         memcpy(init, &hi, sizeof(hi));
         PairParams<T> pp;
-        pp.h = h; pp.cstart = ccount; pp.tcstart = tccount; pp.spos = spos; pp.scode = scode; pp.tpos = tpos;
+        pp.h = h; pp.cstart = ccount; pp.tcstart = tccount; pp.spos = spos; pp.scode = scode; pp.smeta = smeta; pp.hitmask = hitmask; pp.tpos = tpos;
         pp.tmeta = tmeta; pp.tcount = tcount; pp.toffset = toffset; pp.r2 = (T)radius * (T)radius;
         memcpy(init + RG_PARAMS_OFFSET, &pp, sizeof(pp));
     }
@@ -1072,12 +1243,12 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
         N, Nt, targets, g, posw, h, ccount, cfill, tccount, tcfill, skey, scell, tkey, tcell);
     const int64_t nf = std::max(src_cap, Nt);
     rg_bin_finalize_kernel<T><<<(unsigned)((nf + 255) / 256), 256, 0, stream>>>(
-        N, Nt, targets, g, posw, aff, h, ccount, tccount, skey, scell, tkey, tcell, spos, scode, tpos, tmeta);
+        N, Nt, targets, g, posw, aff, h, ccount, tccount, skey, scell, tkey, tcell, spos, scode, smeta, tpos, tmeta);
 
     const int smem = PAIR_WARPS * PAIR_WARP_BYTES;
     DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_COUNT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int grid = sm_count_cached() * 4;
-    rg_pair_kernel<T, MODE_COUNT><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, nullptr, nullptr, nullptr, 0, HaloArgs{});
+    rg_pair_kernel<T, MODE_COUNT><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, nullptr, nullptr, nullptr, 0, HaloArgs{}, 0);
     rg_post_count_kernel<T><<<(unsigned)((Nt + 255) / 256), 256, 0, stream>>>(Nt, tpos, tcount, counts_out, h);
     DYNB_CUDA_OK((exclusive_scan<uint32_t, long long>(tcount, toffset, nullptr, Nt + 1, sums64,
                                                        reinterpret_cast<long long*>(&h->E), stream)));
@@ -1095,8 +1266,17 @@ static int rg_fill(const void* ws, int64_t* ei, float* shifts, void* d2out, int6
     const int smem = PAIR_WARPS * PAIR_WARP_BYTES;
     DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_FILL>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int grid = sm_count_cached() * 4;
+    // Without distances the edges can come from the hit masks of the counting pass; which of the two
+    // kernels does the work is decided on the device (header word written by the counting pass), the
+    // other one returns at once.
+    const int use_masks = (d2out == nullptr) ? 1 : 0;
+    if (use_masks) {
+        const int fsmem = PAIR_WARPS * FM_WARP_BYTES;
+        DYNB_CUDA_OK(cudaFuncSetAttribute(rg_fillmask_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, fsmem));
+        rg_fillmask_kernel<T><<<grid, PAIR_THREADS, fsmem, stream>>>(params_dev, reinterpret_cast<long long*>(ei), shifts, (long long)E);
+    }
     rg_pair_kernel<T, MODE_FILL><<<grid, PAIR_THREADS, smem, stream>>>(
-        params_dev, reinterpret_cast<long long*>(ei), shifts, static_cast<T*>(d2out), (long long)E, HaloArgs{});
+        params_dev, reinterpret_cast<long long*>(ei), shifts, static_cast<T*>(d2out), (long long)E, HaloArgs{}, use_masks);
     DYNB_CUDA_OK(cudaGetLastError());
     return DYNB_OK;
 }
@@ -1109,7 +1289,7 @@ static int rg_halo_mark(const void* ws, const HaloArgs& ha, cudaStream_t stream)
     const int smem = PAIR_WARPS * PAIR_WARP_BYTES;
     DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_HALO>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int grid = sm_count_cached() * 4;
-    rg_pair_kernel<T, MODE_HALO><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, nullptr, nullptr, nullptr, 0, ha);
+    rg_pair_kernel<T, MODE_HALO><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, nullptr, nullptr, nullptr, 0, ha, 0);
     DYNB_CUDA_OK(cudaGetLastError());
     return DYNB_OK;
 }
