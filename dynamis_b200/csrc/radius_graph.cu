@@ -579,7 +579,30 @@ constexpr int PAIR_THREADS = PAIR_WARPS * 32;
 constexpr int PAIR_CAND_BYTES = 5120;  // dense candidate records per warp (320 float4 / 160 double4)
 constexpr int PAIR_CODE_BYTES = 1280;  // packed shift code per candidate (up to 320)
 constexpr int PAIR_LIST = 128;         // parked hits per target (uint16 each, two targets per warp)
-constexpr int PAIR_WARP_BYTES = PAIR_CAND_BYTES + PAIR_CODE_BYTES + PAIR_LIST * 4;
+constexpr int RUN_FLAG_WORDS = 16;     // run-start bitmap of one staged chunk (up to 512 records)
+constexpr int RUN_INDEX_BYTES = 32 * 4 + RUN_FLAG_WORDS * 4;
+constexpr int PAIR_WARP_BYTES = PAIR_CAND_BYTES + PAIR_CODE_BYTES + PAIR_LIST * 4 + RUN_INDEX_BYTES;
+
+// Flattened candidate list of a warp: lane r owns source run r (run_a = first record, run_off = place
+// of the run in the flattened list).  To find the record behind flattened index jj, the non-empty
+// runs are compacted into delta[] (record = delta[rank] + jj) and every chunk of the list gets a bitmap
+// of the places where a run starts; the rank of the run that covers jj is then a population count.
+__device__ __forceinline__ void runs_compact(int* delta, int run_a, int run_off, int run_len, uint32_t lt)
+{
+    const uint32_t nem = __ballot_sync(0xffffffffu, run_len > 0);
+    if (run_len > 0) delta[__popc(nem & lt)] = run_a - run_off;
+}
+// returns the number of non-empty runs that start before cbeg; flags covers [cbeg, cbeg + 32 * RUN_FLAG_WORDS)
+__device__ __forceinline__ int runs_flags(uint32_t* flags, int run_off, int run_len, int lane, int cbeg)
+{
+    if (lane < RUN_FLAG_WORDS) flags[lane] = 0u;
+    __syncwarp();
+    const int rel = run_off - cbeg;
+    if (run_len > 0 && rel >= 0 && rel < 32 * RUN_FLAG_WORDS) atomicOr(&flags[rel >> 5], 1u << (rel & 31));
+    const uint32_t before = __ballot_sync(0xffffffffu, run_len > 0 && rel < 0);
+    __syncwarp();
+    return __popc(before);
+}
 
 enum { MODE_COUNT = 0, MODE_FILL = 1, MODE_HALO = 2 };
 
@@ -629,6 +652,9 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
     uint32_t* codes = reinterpret_cast<uint32_t*>(wbase + PAIR_CAND_BYTES);
     unsigned short* listA = reinterpret_cast<unsigned short*>(wbase + PAIR_CAND_BYTES + PAIR_CODE_BYTES);
     unsigned short* listB = listA + PAIR_LIST;
+    int* delta = reinterpret_cast<int*>(wbase + PAIR_CAND_BYTES + PAIR_CODE_BYTES + PAIR_LIST * 4);
+    uint32_t* flags = reinterpret_cast<uint32_t*>(delta + 32);
+    const uint32_t le = lanemask_lt() | (1u << (threadIdx.x & 31));
 
     DevHeader* hp = p.h;
     if (hp->status & RG_FATAL) return;
@@ -678,6 +704,8 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
         int L;
         const int run_off = warp_excl_scan(run_len, lane, &L);
         const int nslots_total = (L + 31) >> 5;
+        __syncwarp();
+        runs_compact(delta, run_a, run_off, run_len, lt);
         const bool write_masks = (MODE == MODE_COUNT) && nslots_total <= RG_MASK_SLOTS;
         warp_max_slots = max(warp_max_slots, nslots_total);
 
@@ -685,20 +713,15 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
             const int clen = min(CAP, L - cbeg);
             const int clen32 = (clen + 31) & ~31;
             const bool more_chunks = cbeg + CAP < L;
-            __syncwarp();
-            // dense staging: slot j of the list holds flattened candidate cbeg + j; every lane finds the
-            // run of its candidate by a shuffle binary search, so all loads of a chunk are independent
-            for (int j = lane; j < clen32; j += 32) {
-                const int jj = cbeg + j;
-                int r = 0;
-#pragma unroll
-                for (int step = 16; step >= 1; step >>= 1) {
-                    const int cr = r + step;
-                    const int o = __shfl_sync(0xffffffffu, run_off, cr & 31);
-                    if (cr < 32 && o <= jj) r = cr;
-                }
-                const int gidx = __shfl_sync(0xffffffffu, run_a, r) + (jj - __shfl_sync(0xffffffffu, run_off, r));
+            // dense staging: slot j of the list holds flattened candidate cbeg + j; all loads of a chunk are
+            // independent
+            int rank_base = runs_flags(flags, run_off, run_len, lane, cbeg);
+            for (int j = lane, sw = 0; j < clen32; j += 32, sw++) {
+                const uint32_t word = flags[sw];
+                const int r = rank_base + __popc(word & le) - 1;
+                rank_base += __popc(word);
                 if (j < clen) {
+                    const int gidx = delta[r] + cbeg + j;
                     cand[j] = p.spos[gidx];  // w = atom id
                     if (MODE == MODE_FILL) codes[j] = p.scode[gidx];
                 }
@@ -882,7 +905,7 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
 // loaded and no distance is recomputed, and the edge order is the one rg_pair_kernel<FILL> gives.
 // ------------------------------------------------------------------------------------------
 constexpr int FM_META = RG_MASK_SLOTS * 32;                       // staged candidate records per warp
-constexpr int FM_WARP_BYTES = FM_META * 8 + FM_META * 2;    // records + one parked slot per possible hit
+constexpr int FM_WARP_BYTES = FM_META * 8 + FM_META * 2 + RUN_INDEX_BYTES;    // records + one parked slot per possible hit
 
 template <typename T>
 __global__ void __launch_bounds__(PAIR_THREADS, 4)
@@ -895,6 +918,9 @@ rg_fillmask_kernel(const PairParams<T>* __restrict__ params_dev, long long* __re
     unsigned char* wbase = smem_raw + warp * FM_WARP_BYTES;
     uint2* meta = reinterpret_cast<uint2*>(wbase);
     unsigned short* list = reinterpret_cast<unsigned short*>(wbase + FM_META * 8);
+    int* delta = reinterpret_cast<int*>(wbase + FM_META * 8 + FM_META * 2);
+    uint32_t* flags = reinterpret_cast<uint32_t*>(delta + 32);
+    const uint32_t le = lanemask_lt() | (1u << (threadIdx.x & 31));
 
     const DevHeader* hp = p.h;
     if (hp->status & RG_FATAL) return;
@@ -941,16 +967,13 @@ rg_fillmask_kernel(const PairParams<T>* __restrict__ params_dev, long long* __re
         if (nslots == 0) continue;
 
         __syncwarp();
-        for (int j = lane; j < nslots * 32; j += 32) {
-            int r = 0;
-#pragma unroll
-            for (int step = 16; step >= 1; step >>= 1) {
-                const int cr = r + step;
-                const int o = __shfl_sync(0xffffffffu, run_off, cr & 31);
-                if (cr < 32 && o <= j) r = cr;
-            }
-            const int gidx = __shfl_sync(0xffffffffu, run_a, r) + (j - __shfl_sync(0xffffffffu, run_off, r));
-            if (j < L) meta[j] = p.smeta[gidx];
+        runs_compact(delta, run_a, run_off, run_len, lt);
+        int rank_base = runs_flags(flags, run_off, run_len, lane, 0);
+        for (int j = lane, sw = 0; sw < nslots; j += 32, sw++) {
+            const uint32_t word = flags[sw];
+            const int r = rank_base + __popc(word & le) - 1;
+            rank_base += __popc(word);
+            if (j < L) meta[j] = p.smeta[delta[r] + j];
         }
         __syncwarp();
 
