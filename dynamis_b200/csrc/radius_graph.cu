@@ -579,6 +579,10 @@ constexpr int PAIR_THREADS = PAIR_WARPS * 32;
 constexpr int PAIR_CAND_BYTES = 5120;  // dense candidate records per warp (320 float4 / 160 double4)
 constexpr int PAIR_CODE_BYTES = 1280;  // packed shift code per candidate (up to 320)
 constexpr int PAIR_LIST = 128;         // parked hits per target (uint16 each, two targets per warp)
+// The pair kernels are launched with this many times the CTAs that fit the device at once: SMs do not
+// all drain their share at the same speed, and a static one-wave split left the slowest SM 20-30 %
+// behind the average; with several short waves the block scheduler evens that out.
+constexpr int PAIR_GRID_WAVES = 8;
 constexpr int RUN_FLAG_WORDS = 16;     // run-start bitmap of one staged chunk (up to 512 records)
 constexpr int RUN_INDEX_BYTES = 32 * 4 + RUN_FLAG_WORDS * 4;
 constexpr int PAIR_WARP_BYTES = PAIR_CAND_BYTES + PAIR_CODE_BYTES + PAIR_LIST * 4 + RUN_INDEX_BYTES;
@@ -893,8 +897,8 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                 for (uint32_t t = tb[yr] + lane; t < te[yr]; t += 32) p.tcount[t] = 0;
         }
     }
-    // longest candidate list of any group with targets, in 32-record slots (one atomic per warp)
-    if (MODE == MODE_COUNT && lane == 0 && warp_max_slots > 0) atomicMax(&hp->reserved[0], (long long)warp_max_slots);
+    // a candidate list too long for the hit bits: the edge writer has to recompute distances
+    if (MODE == MODE_COUNT && lane == 0 && warp_max_slots > RG_MASK_SLOTS) atomicMax(&hp->reserved[0], (long long)warp_max_slots);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -933,33 +937,55 @@ rg_fillmask_kernel(const PairParams<T>* __restrict__ params_dev, long long* __re
     const int lane_dy = (lane % Wy) - pad, lane_dz = (lane / Wy) - pad;
     const uint32_t lt = lanemask_lt();
 
-    const uint32_t nwarps = gridDim.x * PAIR_WARPS;
-    for (uint32_t grp = blockIdx.x * PAIR_WARPS + warp; grp < num_groups; grp += nwarps) {
+    // target ranges and source run of a group; the next group's are requested while the current group
+    // is written, so that one round trip to memory per group (the candidate records) stays exposed
+    struct GroupDesc { uint32_t tb0, te0, tb1, te1; int run_a, run_len; };
+    auto fetch = [&](uint32_t grp) -> GroupDesc {
+        GroupDesc d;
         const uint32_t row = grp / gx;
         const int ix = (int)(grp - row * gx);
         const int cz = (int)(row / gy), iy = (int)(row - (uint32_t)cz * gy);
         const int cx0 = ix * S, cx1 = min(cx0 + S, nx) - 1;
         const int cy0 = iy * Sy, cy1 = min(cy0 + Sy, ny) - 1;
-        uint32_t tb[2], te[2];
-        tb[0] = p.tcstart[((uint32_t)cz * ny + cy0) * nx + cx0];
-        te[0] = p.tcstart[((uint32_t)cz * ny + cy0) * nx + cx1 + 1];
-        tb[1] = te[1] = 0;
+        d.tb0 = p.tcstart[((uint32_t)cz * ny + cy0) * nx + cx0];
+        d.te0 = p.tcstart[((uint32_t)cz * ny + cy0) * nx + cx1 + 1];
+        d.tb1 = d.te1 = 0;
         if (cy1 > cy0) {
-            tb[1] = p.tcstart[((uint32_t)cz * ny + cy1) * nx + cx0];
-            te[1] = p.tcstart[((uint32_t)cz * ny + cy1) * nx + cx1 + 1];
+            d.tb1 = p.tcstart[((uint32_t)cz * ny + cy1) * nx + cx0];
+            d.te1 = p.tcstart[((uint32_t)cz * ny + cy1) * nx + cx1 + 1];
         }
-        if (tb[0] == te[0] && tb[1] == te[1]) continue;
-
-        int run_a = 0, run_len = 0;
+        d.run_a = 0;
+        d.run_len = 0;
         if (lane < nrun) {
             const int yy = cy0 + lane_dy, zz = cz + lane_dz;
             if (yy >= 0 && yy < ny && yy <= cy1 + pad && zz >= 0 && zz < nz) {
                 const uint32_t b = ((uint32_t)zz * ny + yy) * nx;
                 const uint32_t a = p.cstart[b + max(cx0 - pad, 0)];
                 const uint32_t e = p.cstart[b + min(cx1 + pad, nx - 1) + 1];
-                run_a = (int)a;
-                run_len = (int)(e - a);
+                d.run_a = (int)a;
+                d.run_len = (int)(e - a);
             }
+        }
+        return d;
+    };
+
+    const uint32_t nwarps = gridDim.x * PAIR_WARPS;
+    uint32_t grp = blockIdx.x * PAIR_WARPS + warp;
+    if (grp >= num_groups) return;
+    GroupDesc nd = fetch(grp);
+    for (; grp < num_groups; grp += nwarps) {
+        const GroupDesc d = nd;
+        if (grp + nwarps < num_groups) nd = fetch(grp + nwarps);
+        uint32_t tb[2] = {d.tb0, d.tb1}, te[2] = {d.te0, d.te1};
+        if (tb[0] == te[0] && tb[1] == te[1]) continue;
+        const int run_a = d.run_a, run_len = d.run_len;
+        // the first target's words do not depend on the candidate records: ask for them now
+        int4 ntm;
+        long long nbase;
+        uint32_t nw;
+        {
+            const uint32_t t = tb[0] != te[0] ? tb[0] : tb[1];
+            ntm = p.tmeta[t]; nbase = p.toffset[t]; nw = p.hitmask[(size_t)t * 32 + lane];
         }
         int L;
         const int run_off = warp_excl_scan(run_len, lane, &L);
@@ -982,13 +1008,6 @@ rg_fillmask_kernel(const PairParams<T>* __restrict__ params_dev, long long* __re
         // a warp scan of the bit counts gives every lane the place of its first edge, so the edges of a
         // target are ordered by (candidate mod 32, candidate / 32).
         const int n0 = (int)(te[0] - tb[0]), nT = n0 + (int)(te[1] - tb[1]);
-        int4 ntm;
-        long long nbase;
-        uint32_t nw;
-        {
-            const uint32_t t = n0 > 0 ? tb[0] : tb[1];
-            ntm = p.tmeta[t]; nbase = p.toffset[t]; nw = p.hitmask[(size_t)t * 32 + lane];
-        }
         for (int q = 0; q < nT; q++) {
             const int4 tm = ntm;
             const long long base = nbase;
@@ -1055,6 +1074,16 @@ __global__ void rg_zero_counts_kernel(int64_t Nt, int32_t* counts_out)
 // ------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------
+static int pair_grid_waves()
+{
+    static const int waves = [] {
+        int w = PAIR_GRID_WAVES;
+        if (const char* env = getenv("DYNB_RG_WAVES")) w = atoi(env);  // tuning knob
+        return std::min(std::max(w, 1), 64);
+    }();
+    return waves;
+}
+
 struct RgLayout {
     int64_t hdr, partials, tpartials, posw, aff, ccount, cfill, tccount, tcfill, skey, scell, spos, scode, smeta, hitmask, tkey, tcell, tpos, tmeta,
         tcount, toffset, sums, total;
@@ -1270,7 +1299,7 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
 
     const int smem = PAIR_WARPS * PAIR_WARP_BYTES;
     DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_COUNT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    const int grid = sm_count_cached() * 4;
+    const int grid = sm_count_cached() * 4 * pair_grid_waves();
     rg_pair_kernel<T, MODE_COUNT><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, nullptr, nullptr, nullptr, 0, HaloArgs{}, 0);
     rg_post_count_kernel<T><<<(unsigned)((Nt + 255) / 256), 256, 0, stream>>>(Nt, tpos, tcount, counts_out, h);
     DYNB_CUDA_OK((exclusive_scan<uint32_t, long long>(tcount, toffset, nullptr, Nt + 1, sums64,
@@ -1288,7 +1317,7 @@ static int rg_fill(const void* ws, int64_t* ei, float* shifts, void* d2out, int6
     const auto* params_dev = reinterpret_cast<const PairParams<T>*>(w + RG_PARAMS_OFFSET);
     const int smem = PAIR_WARPS * PAIR_WARP_BYTES;
     DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_FILL>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    const int grid = sm_count_cached() * 4;
+    const int grid = sm_count_cached() * 4 * pair_grid_waves();
     // Without distances the edges can come from the hit masks of the counting pass; which of the two
     // kernels does the work is decided on the device (header word written by the counting pass), the
     // other one returns at once.
@@ -1311,7 +1340,7 @@ static int rg_halo_mark(const void* ws, const HaloArgs& ha, cudaStream_t stream)
     const auto* params_dev = reinterpret_cast<const PairParams<T>*>(w + RG_PARAMS_OFFSET);
     const int smem = PAIR_WARPS * PAIR_WARP_BYTES;
     DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_HALO>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    const int grid = sm_count_cached() * 4;
+    const int grid = sm_count_cached() * 4 * pair_grid_waves();
     rg_pair_kernel<T, MODE_HALO><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, nullptr, nullptr, nullptr, 0, ha, 0);
     DYNB_CUDA_OK(cudaGetLastError());
     return DYNB_OK;

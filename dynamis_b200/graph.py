@@ -86,7 +86,7 @@ class RadiusGraphPlan:
     valid until the next radius-graph call on the same device, which reuses the workspace.
     """
 
-    __slots__ = ("ws", "dtype_code", "E", "M", "counts", "device", "pos_dtype", "max_degree", "grid", "num_groups", "max_list_slots")
+    __slots__ = ("ws", "dtype_code", "E", "M", "counts", "device", "pos_dtype", "max_degree", "grid", "num_groups")
 
     def fill(self, want_dist_sq: bool = False):
         dev = self.device
@@ -166,7 +166,6 @@ def plan_radius_graph(pos, cell, pbc, radius, target_indices=None) -> RadiusGrap
     plan.max_degree = int(hdr.max_degree)
     plan.grid = (int(hdr.grid[0]), int(hdr.grid[1]), int(hdr.grid[2]))
     plan.num_groups = int(hdr.num_groups)
-    plan.max_list_slots = int(hdr.reserved[0])
     plan.counts = counts
     plan.device = dev
     plan.pos_dtype = pos.dtype
