@@ -274,12 +274,12 @@ def run_ours(args):
     alg_bytes = 28.0 * plan.E
     achieved = alg_bytes / (fill_ms * 1e-3) / 1e9
     traffic = None
-    tp = os.path.join(ROOT, "profiles", "rg_pair_fill_traffic.txt")
+    tp = os.path.join(ROOT, "profiles", "rg_fillmask_traffic.txt")
     if os.path.exists(tp):
         with open(tp) as f:
             tj = json.load(f)
         traffic = tj["dram_bytes_per_edge"] * plan.E
-    roofline = {"bound": "hbm", "kernel": "rg_pair_kernel<float, FILL>", "achieved": achieved, "peak": peak,
+    roofline = {"bound": "hbm", "kernel": "rg_fillmask_kernel<float>", "achieved": achieved, "peak": peak,
                 "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": traffic,
                 "algorithmic_bytes": alg_bytes, "ms_per_launch": fill_ms}
     del ei, sh
