@@ -187,7 +187,7 @@ def run(args, rank: int, world: int, dev: torch.device):
             "nvlink": {"bytes_sent_per_rank_per_step": bytes_rank, "achieved_gbs": bytes_rank / (xms * 1e-3) / 1e9,
                        "peak_gbs": NVLINK_PEER_GBS, "peak_kind": "measured peer copy per direction",
                        "frac": bytes_rank / (xms * 1e-3) / 1e9 / NVLINK_PEER_GBS},
-            "roofline": {"bound": "hbm", "kernel": "rg_pair_kernel<float, FILL> (rank 0)", "achieved": 28.0 * plan.E / (fill_ms * 1e-3) / 1e9,
+            "roofline": {"bound": "hbm", "kernel": "rg_fillmask_kernel<float> (rank 0)", "achieved": 28.0 * plan.E / (fill_ms * 1e-3) / 1e9,
                          "peak": peak, "unit": "GB/s", "frac": 28.0 * plan.E / (fill_ms * 1e-3) / 1e9 / peak, "peak_kind": peak_kind,
                          "traffic": None, "algorithmic_bytes": 28.0 * plan.E, "ms_per_launch": fill_ms},
             "cpu_baseline": None,

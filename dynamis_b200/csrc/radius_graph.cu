@@ -670,7 +670,6 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
     const uint32_t num_groups = (uint32_t)hp->num_groups;  // < 2^31: never more groups than cells
     const int Wd = 2 * pad + 1, Wy = Sy + 2 * pad, nrun = Wy * Wd;
     const int lane_dy = (lane % Wy) - pad, lane_dz = (lane / Wy) - pad;
-    const int sub = lane >> 3, sl = lane & 7;
     const T r2 = p.r2;
     const T eps = (T)1e-8f;
     const uint32_t lt = lanemask_lt();
@@ -1327,7 +1326,9 @@ static int rg_fill(const void* ws, int64_t* ei, float* shifts, void* d2out, int6
         DYNB_CUDA_OK(cudaFuncSetAttribute(rg_fillmask_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, fsmem));
         rg_fillmask_kernel<T><<<grid, PAIR_THREADS, fsmem, stream>>>(params_dev, reinterpret_cast<long long*>(ei), shifts, (long long)E);
     }
-    rg_pair_kernel<T, MODE_FILL><<<grid, PAIR_THREADS, smem, stream>>>(
+    // behind the bit-driven writer this launch is idle in all but unusual inputs: two waves keep its cost low
+    const int fgrid = use_masks ? sm_count_cached() * 4 * std::min(2, pair_grid_waves()) : grid;
+    rg_pair_kernel<T, MODE_FILL><<<fgrid, PAIR_THREADS, smem, stream>>>(
         params_dev, reinterpret_cast<long long*>(ei), shifts, static_cast<T*>(d2out), (long long)E, HaloArgs{}, use_masks);
     DYNB_CUDA_OK(cudaGetLastError());
     return DYNB_OK;

@@ -1,5 +1,6 @@
-// Space-filling-curve partition for B200 (sm_100a): bounds -> keys -> stable LSD radix sort ->
-// contiguous split into W ranks.
+// Space-filling-curve partition for B200 (sm_100a): bounds -> keys -> contiguous split into W ranks,
+// either through a stable LSD radix sort (when the curve-order permutation is wanted) or, for the labels
+// alone, through a digit-by-digit selection of the W - 1 split points (no sort).
 //
 // Replaces sfc_partition_cuda_impl (dynamis_state/src/csrc/partition/sfc_kernels.cu:178-251) and
 // its kernels (:32-173).  The key arithmetic (IEEE division by the range, truncating quantisation,
@@ -54,15 +55,14 @@ sfc_minmax_kernel(const float* __restrict__ pos, int64_t n, SfcBounds* __restric
     }
 }
 
-__global__ void sfc_bounds_finish_kernel(SfcBounds* b)
+// lower bound and range of axis k from the ordered-integer extrema (sfc_kernels.cu:197-198); every
+// thread of the key kernel derives them itself, which saves a one-thread launch in between
+__device__ __forceinline__ void sfc_axis(const SfcBounds* __restrict__ b, int k, float* lo_out, float* range_out)
 {
-    const int k = threadIdx.x;
-    if (k < 3) {
-        const float lo = unordered_f32(b->mn[k]), hi = unordered_f32(b->mx[k]);
-        float range = hi - lo;                       // sfc_kernels.cu:197-198
-        b->pmin[k] = lo;
-        b->prange[k] = (range > 0.0f) ? range : 1.0f;
-    }
+    const float lo = unordered_f32(b->mn[k]), hi = unordered_f32(b->mx[k]);
+    const float range = hi - lo;
+    *lo_out = lo;
+    *range_out = (range > 0.0f) ? range : 1.0f;
 }
 
 // ------------------------------------------------------------------------------------------ keys
@@ -84,9 +84,13 @@ sfc_keys_kernel(const float* __restrict__ pos, int64_t n, const SfcBounds* __res
 {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const float nx = (pos[i * 3 + 0] - b->pmin[0]) / b->prange[0];
-    const float ny = (pos[i * 3 + 1] - b->pmin[1]) / b->prange[1];
-    const float nz = (pos[i * 3 + 2] - b->pmin[2]) / b->prange[2];
+    float lo0, lo1, lo2, rg0, rg1, rg2;
+    sfc_axis(b, 0, &lo0, &rg0);
+    sfc_axis(b, 1, &lo1, &rg1);
+    sfc_axis(b, 2, &lo2, &rg2);
+    const float nx = (pos[i * 3 + 0] - lo0) / rg0;
+    const float ny = (pos[i * 3 + 1] - lo1) / rg1;
+    const float nz = (pos[i * 3 + 2] - lo2) / rg2;
     uint64_t key;
     if (CURVE == 0) {
         const uint32_t grid_max = (1u << 21) - 1;
@@ -295,7 +299,271 @@ __global__ void __launch_bounds__(256) u32_to_i64_kernel(const uint32_t* a, int6
     if (i < n) b[i] = (int64_t)a[i];
 }
 
-struct SfcLayout { int64_t bounds, keys, idx, sorted_w, excl, total_w, sums, rs, total; };
+
+// ------------------------------------------------------------------------------------------ labels by selection
+// When only the labels are wanted (no curve-order permutation), the sort is not needed: an atom's
+// label is the number of split points at or before it in (key, atom index) order, and the W - 1 split
+// points — for label p the first atom, in that order, whose inclusive prefix weight reaches
+// ceil(p * total / W) (unit weights: the atom of rank first_rank(p)) — are found by a most-significant-
+// digit descent on the composite number C = key << idx_bits | index.  Every level is a weighted digit
+// histogram of the atoms that still share a split point's prefix (one pass over the keys, atomics on a
+// table in L2) and one block per split point that walks the histogram to the digit where its threshold
+// is crossed.  Six levels of 16 bits cover Morton keys of a million atoms: 12 small launches instead
+// of the 40 of the eight radix passes, and nothing but the keys is read.
+// Weights must be non-negative here (degrees); the labels are those of the sorted path.
+typedef unsigned __int128 u128;
+constexpr int SEL_MAX_SPLITS = 1024;
+constexpr int64_t SEL_HIST_BYTES = 4ll << 20;  // per buffer (two buffers)
+
+struct SelSplit {           // one per split point and level parity
+    unsigned long long pre_hi, pre_lo;  // C >> (bits not yet decided)
+    long long residual;                 // weight still to cover among the atoms that share the prefix
+    int dead;                           // its threshold lies beyond the total weight: no atom reaches it
+    int pad;
+};
+
+__device__ __forceinline__ u128 sel_prefix(const SelSplit& s) { return ((u128)s.pre_hi << 64) | (u128)s.pre_lo; }
+
+// Distinct prefixes of the live split points (they are non-decreasing) into glist (loaded by the whole
+// block, compacted in place).  All threads of the block call this; returns the number of groups.
+__device__ int sel_groups(const SelSplit* __restrict__ st, int nsplit, u128* glist, int* gid_of_split)
+{
+    __shared__ int s_ng;
+    __shared__ int s_live;
+    if (threadIdx.x == 0) s_live = nsplit;
+    __syncthreads();
+    for (int s = threadIdx.x; s < nsplit; s += blockDim.x) {
+        const SelSplit v = st[s];
+        glist[s] = sel_prefix(v);
+        if (v.dead) atomicMin(&s_live, s);  // dead split points are the last ones
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int ng = 0;
+        const int live = s_live;
+        for (int s = 0; s < live; s++) {
+            const u128 p = glist[s];  // ng <= s: the compaction never overtakes the read
+            if (ng == 0 || glist[ng - 1] != p) glist[ng++] = p;
+            if (gid_of_split) gid_of_split[s] = ng - 1;
+        }
+        if (gid_of_split)
+            for (int s = live; s < nsplit; s++) gid_of_split[s] = -1;
+        s_ng = ng;
+    }
+    __syncthreads();
+    return s_ng;
+}
+
+// A warp finds, among up to 256 counters at p, the first whose inclusive prefix reaches R: returns its
+// index to all lanes (-1 if the sum stays below R), *before = weight in front of it, *total = sum of all.
+__device__ int sel_warp_cross(const unsigned long long* p, int count, long long R, long long* before, long long* total)
+{
+    const int lane = threadIdx.x & 31;
+    long long v[8];
+    long long local = 0;
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        const int i = lane * 8 + k;
+        v[k] = (i < count) ? (long long)__ldcg(p + i) : 0ll;  // counters were written by atomics: read them at L2
+        local += v[k];
+    }
+    long long x = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const long long y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
+    }
+    *total = __shfl_sync(0xffffffffu, x, 31);
+    const bool mine = (x - local < R) && (R <= x);
+    const unsigned m = __ballot_sync(0xffffffffu, mine);
+    if (m == 0u) return -1;
+    int idx = -1;
+    long long bef = 0, c = x - local;
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        if (idx < 0 && c + v[k] >= R) { idx = lane * 8 + k; bef = c; }
+        c += v[k];
+    }
+    const int src = __ffs((int)m) - 1;
+    *before = __shfl_sync(0xffffffffu, bef, src);
+    return __shfl_sync(0xffffffffu, idx, src);
+}
+
+// One warp advances split point s by one level: coarse counters -> run of digits -> the digit where its
+// threshold is crossed.  gid: group of every split point at this level (not read at level 0).
+__device__ void sel_pick_warp(int s, const SelSplit* __restrict__ st_in, SelSplit* __restrict__ st_out, const int* gid,
+                              int nsplit, int level, int width, int dbits, int64_t n, int64_t W, int weighted,
+                              const unsigned long long* hist)
+{
+    const int lane = threadIdx.x & 31;
+    SelSplit me;
+    int g = 0;
+    if (level == 0) {
+        me.pre_hi = me.pre_lo = 0; me.residual = 0; me.dead = 0; me.pad = 0;
+    } else {
+        me = st_in[s];
+        g = gid[s];
+        if (me.dead) {
+            if (lane == 0) st_out[s] = me;
+            return;
+        }
+    }
+    const unsigned long long* fine = hist + ((size_t)g << dbits);
+    const unsigned long long* coarse = hist + ((size_t)nsplit << dbits) + ((size_t)g << 8);
+    const int fbits = min(width, 8);
+    const int nc = 1 << (width - fbits);  // coarse counters in use (<= 256)
+    long long R = me.residual;
+    long long before_c = 0, before_f = 0, total = 0;
+    int cb;
+    if (level == 0) {
+        // the total first: thresholds of sfc_kernels.cu:123-134 (equal counts) and :165-170 (weights)
+        sel_warp_cross(coarse, nc, 0x7fffffffffffffffll, &before_c, &total);
+        const long long p = s + 1;
+        long long T;
+        if (weighted) {
+            T = (total > 0) ? (long long)(((u128)p * (u128)total + (u128)(W - 1)) / (u128)W) : total + 1;
+            if (T < 1) T = 1;
+        } else {
+            const long long base = n / W, rem = n % W;
+            const long long first = (p <= rem) ? p * (base + 1) : rem * (base + 1) + (p - rem) * base;
+            T = first + 1;
+        }
+        me.residual = R = T;
+        me.dead = (T > total) ? 1 : 0;
+        if (me.dead) {
+            if (lane == 0) st_out[s] = me;
+            return;
+        }
+    }
+    cb = sel_warp_cross(coarse, nc, R, &before_c, &total);
+    if (cb < 0) return;  // cannot happen: the threshold lies inside this group
+    const int fb = sel_warp_cross(fine + ((size_t)cb << fbits), 1 << fbits, R - before_c, &before_f, &total);
+    if (fb < 0) return;
+    if (lane == 0) {
+        const unsigned digit = ((unsigned)cb << fbits) | (unsigned)fb;
+        const u128 P = (sel_prefix(me) << width) | (u128)digit;
+        me.pre_hi = (unsigned long long)(P >> 64);
+        me.pre_lo = (unsigned long long)P;
+        me.residual = R - before_c - before_f;
+        st_out[s] = me;
+    }
+}
+
+// Table of one level: per group 2^dbits digit counters ("fine"), followed by per group 256 coarse
+// counters, one per run of 2^fbits consecutive digits (fbits = min(width, 8)), so that a split point is
+// located by reading 256 + 256 counters instead of the whole digit range.
+// With done_counter != nullptr the block that finishes last also advances the split points (one warp
+// each), which saves a launch per level; used while there are few split points.
+__global__ void __launch_bounds__(256)
+sel_hist_kernel(const uint64_t* __restrict__ keys, const int64_t* __restrict__ weights, int64_t n, int idx_bits,
+                int shift, int width, int dbits, const SelSplit* __restrict__ st, SelSplit* __restrict__ st_out, int nsplit,
+                int level, int64_t W, unsigned long long* __restrict__ hist, unsigned long long* __restrict__ hist_next,
+                int64_t table_words, unsigned int* __restrict__ done_counter)
+{
+    __shared__ u128 glist[SEL_MAX_SPLITS];
+    __shared__ int gid[SEL_MAX_SPLITS];
+    __shared__ unsigned long long s_coarse[256];
+    __shared__ bool s_last;
+    // clear the table the next level accumulates into (its last reader, the previous pick, has finished)
+    for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < table_words; k += (int64_t)gridDim.x * blockDim.x)
+        hist_next[k] = 0ull;
+    unsigned long long* coarse = hist + ((size_t)nsplit << dbits);
+    const int fbits = min(width, 8);
+    int ng = 1;
+    if (level == 0) {
+        if (threadIdx.x == 0) glist[0] = 0;
+        s_coarse[threadIdx.x] = 0ull;  // one group, every atom counts: coarse counters through shared memory
+        __syncthreads();
+    } else {
+        ng = sel_groups(st, nsplit, glist, gid);
+    }
+    const u128 dmask = ((u128)1 << width) - 1;
+    if (ng > 0) {
+        for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+            const u128 C = ((u128)keys[i] << idx_bits) | (u128)(uint64_t)i;
+            const u128 P = C >> (shift + width);
+            int lo = 0, hi = ng;  // first group with prefix >= P
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (glist[mid] < P) lo = mid + 1; else hi = mid;
+            }
+            if (lo < ng && glist[lo] == P) {
+                const unsigned long long w = weights ? (unsigned long long)weights[i] : 1ull;
+                if (w) {
+                    const unsigned digit = (unsigned)((C >> shift) & dmask);
+                    atomicAdd(&hist[((size_t)lo << dbits) + digit], w);
+                    if (level == 0) atomicAdd(&s_coarse[digit >> fbits], w);
+                    else atomicAdd(&coarse[((size_t)lo << 8) + (digit >> fbits)], w);
+                }
+            }
+        }
+    }
+    if (level == 0) {
+        __syncthreads();
+        const unsigned long long v = s_coarse[threadIdx.x];
+        if (v) atomicAdd(&coarse[threadIdx.x], v);
+    }
+    if (done_counter == nullptr) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(done_counter, 1u) == gridDim.x - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int s = threadIdx.x >> 5; s < nsplit; s += (int)(blockDim.x >> 5))
+        sel_pick_warp(s, st, st_out, gid, nsplit, level, width, dbits, n, W, weights != nullptr ? 1 : 0, hist);
+}
+
+// the same step as its own launch, eight split points per block (many split points)
+__global__ void __launch_bounds__(256)
+sel_pick_kernel(const SelSplit* __restrict__ st_in, SelSplit* __restrict__ st_out, int nsplit, int level, int width, int dbits,
+                int64_t n, int64_t W, int weighted, const unsigned long long* __restrict__ hist)
+{
+    __shared__ u128 glist[SEL_MAX_SPLITS];
+    __shared__ int gid[SEL_MAX_SPLITS];
+    if (level > 0) sel_groups(st_in, nsplit, glist, gid);
+    const int s = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (s < nsplit) sel_pick_warp(s, st_in, st_out, gid, nsplit, level, width, dbits, n, W, weighted, hist);
+}
+
+__global__ void __launch_bounds__(256)
+sel_label_kernel(const uint64_t* __restrict__ keys, int64_t n, int idx_bits, const SelSplit* __restrict__ st, int nsplit,
+                 int64_t* __restrict__ labels)
+{
+    __shared__ u128 cs[SEL_MAX_SPLITS];
+    __shared__ int s_live;
+    if (threadIdx.x == 0) s_live = nsplit;
+    __syncthreads();
+    for (int s = threadIdx.x; s < nsplit; s += blockDim.x) {
+        const SelSplit v = st[s];
+        cs[s] = sel_prefix(v);
+        if (v.dead) atomicMin(&s_live, s);  // dead split points are the last ones
+    }
+    __syncthreads();
+    const int live = s_live;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const u128 C = ((u128)keys[i] << idx_bits) | (u128)(uint64_t)i;
+        int lo = 0, hi = live;  // number of split points <= C
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (cs[mid] <= C) lo = mid + 1; else hi = mid;
+        }
+        labels[i] = (int64_t)lo;
+    }
+}
+
+// digit width: the widest the table budget allows for W - 1 groups, then narrowed while the number
+// of levels stays the same (a narrower digit means a smaller table to clear per level)
+static int sel_digit_bits(int64_t W, int total_bits)
+{
+    int d = 16;
+    while (d > 8 && (int64_t)(W - 1) * (((int64_t)8 << d) + 2048) + 256 > SEL_HIST_BYTES) d--;
+    const int levels = (total_bits + d - 1) / d;
+    while (d > 8 && (total_bits + (d - 1) - 1) / (d - 1) == levels) d--;
+    return d;
+}
+
+struct SfcLayout { int64_t bounds, keys, idx, sorted_w, excl, total_w, sums, rs, total_sort, sel_state, sel_hist, total; };
 static SfcLayout sfc_layout(int64_t n)
 {
     SfcLayout L;
@@ -309,6 +577,9 @@ static SfcLayout sfc_layout(int64_t n)
     L.total_w = take(64);
     L.sums = take((int64_t)(scan_num_tiles(n) + 1) * 8);
     L.rs = take(rs_layout(n).total);
+    L.total_sort = o;  // enough for the sorted path
+    L.sel_state = take(2 * SEL_MAX_SPLITS * (int64_t)sizeof(SelSplit));
+    L.sel_hist = take(2 * SEL_HIST_BYTES);
     L.total = o;
     return L;
 }
@@ -322,7 +593,6 @@ static int sfc_keys_into(const float* pos, int64_t n, int curve, unsigned char* 
     DYNB_CUDA_OK(cudaMemcpyAsync(b, &init, sizeof(init), cudaMemcpyHostToDevice, stream));
     const int grid = (int)std::min<int64_t>((n + 255) / 256, (int64_t)sm_count_cached() * 4);
     sfc_minmax_kernel<<<grid, 256, 0, stream>>>(pos, n, b);
-    sfc_bounds_finish_kernel<<<1, 32, 0, stream>>>(b);
     const unsigned nbk = (unsigned)((n + 255) / 256);
     if (curve == 0) sfc_keys_kernel<0><<<nbk, 256, 0, stream>>>(pos, n, b, keys, idx);
     else sfc_keys_kernel<1><<<nbk, 256, 0, stream>>>(pos, n, b, keys, idx);
@@ -370,10 +640,48 @@ extern "C" int dynb_sfc_partition(const float* pos_dev, int64_t n_atoms, const i
         return DYNB_OK;
     }
     const SfcLayout L = sfc_layout(n_atoms);
-    if (workspace_bytes < L.total) return fail_arg("workspace too small (see dynb_sfc_workspace_bytes)");
+    if (workspace_bytes < L.total_sort) return fail_arg("workspace too small (see dynb_sfc_workspace_bytes)");
     unsigned char* ws = static_cast<unsigned char*>(workspace_dev);
     uint64_t* keys = reinterpret_cast<uint64_t*>(ws + L.keys);
     uint32_t* idx = reinterpret_cast<uint32_t*>(ws + L.idx);
+    static const bool force_sort = getenv("DYNB_SFC_SORT") != nullptr;  // testing knob: always take the sorted path
+    if (perm_dev == nullptr && W >= 2 && W - 1 <= SEL_MAX_SPLITS && workspace_bytes >= L.total && !force_sort) {
+        // labels by selection (no sort)
+        int rc = sfc_keys_into(pos_dev, n_atoms, curve_type, ws, L, keys, nullptr, s);
+        if (rc) return rc;
+        const int nsplit = (int)(W - 1);
+        int idx_bits = 1;
+        while (idx_bits < 32 && ((int64_t)1 << idx_bits) < n_atoms) idx_bits++;
+        const int B = (curve_type == 0 ? 63 : 21) + idx_bits;
+        const int dbits = sel_digit_bits(W, B);
+        const int levels = (B + dbits - 1) / dbits;
+        SelSplit* st = reinterpret_cast<SelSplit*>(ws + L.sel_state);
+        unsigned long long* hist = reinterpret_cast<unsigned long long*>(ws + L.sel_hist);
+        const int64_t hist_words = SEL_HIST_BYTES / 8;
+        const int64_t table_words = ((int64_t)nsplit << dbits) + ((int64_t)nsplit << 8);  // digit + coarse counters of a level
+        // the first table and, behind it, one arrival counter per level
+        unsigned int* counters = reinterpret_cast<unsigned int*>(hist + table_words);
+        DYNB_CUDA_OK(cudaMemsetAsync(hist, 0, (size_t)table_words * 8 + 256, s));
+        const bool fused = nsplit <= 16;  // two rounds of eight warps in the last block
+        const int hgrid = (int)std::min<int64_t>((n_atoms + 255) / 256, (int64_t)sm_count_cached() * 4);  // one wave
+        for (int l = 0; l < levels; l++) {
+            const int width = std::min(dbits, B - l * dbits);
+            const int shift = B - l * dbits - width;
+            const SelSplit* st_in = st + (size_t)(l & 1) * SEL_MAX_SPLITS;
+            SelSplit* st_out = st + (size_t)((l + 1) & 1) * SEL_MAX_SPLITS;
+            unsigned long long* h_cur = hist + (size_t)(l & 1) * hist_words;
+            unsigned long long* h_other = hist + (size_t)((l + 1) & 1) * hist_words;
+            unsigned int* done = fused ? counters + l : nullptr;
+            sel_hist_kernel<<<hgrid, 256, 0, s>>>(keys, weights_dev, n_atoms, idx_bits, shift, width, dbits, st_in, st_out, nsplit, l, W,
+                                                  h_cur, h_other, table_words, done);
+            if (!fused)
+                sel_pick_kernel<<<(nsplit + 7) / 8, 256, 0, s>>>(st_in, st_out, nsplit, l, width, dbits, n_atoms, W,
+                                                                 weights_dev != nullptr ? 1 : 0, h_cur);
+        }
+        sel_label_kernel<<<hgrid, 256, 0, s>>>(keys, n_atoms, idx_bits, st + (size_t)(levels & 1) * SEL_MAX_SPLITS, nsplit, labels_dev);
+        DYNB_CUDA_OK(cudaGetLastError());
+        return DYNB_OK;
+    }
     int rc = sfc_keys_into(pos_dev, n_atoms, curve_type, ws, L, keys, idx, s);
     if (rc) return rc;
     rc = rs_sort_pairs(keys, idx, n_atoms, 0, curve_type == 0 ? 64 : 24, ws + L.rs, s);
@@ -440,7 +748,7 @@ extern "C" int dynb_sfc_partition_static(const float* pos_dev, int64_t n_atoms, 
     if (n_atoms > DYNB_SFC_STATIC_MAX_ATOMS_C)
         return dynb::fail_arg("dynb_sfc_partition_static: n_atoms exceeds the built-in scratch (limit 131072 atoms); "
                               "use dynb_sfc_partition with a caller-provided workspace");
-    if (dynb::sfc_layout(std::max<int64_t>(n_atoms, 1)).total > DYNB_SFC_STATIC_BYTES)
+    if (dynb::sfc_layout(std::max<int64_t>(n_atoms, 1)).total_sort > DYNB_SFC_STATIC_BYTES)
         return dynb::fail_arg("dynb_sfc_partition_static: built-in scratch too small for this size");
     int dev = 0;
     DYNB_CUDA_OK(cudaGetDevice(&dev));

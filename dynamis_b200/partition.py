@@ -51,9 +51,11 @@ class SFCCurveType(enum.IntEnum):
 
 
 def launches_per_partition() -> int:
-    """Kernels one Morton partition launches: bounds (2), keys (1), 8 radix passes x (histogram +
-    3 scan kernels + scatter), assignment (1)."""
-    return 2 + 1 + 8 * 5 + 1
+    """Kernels one Morton partition of a million atoms into 8 labels launches (labels only): bounds (1),
+    keys (1), 6 digit levels (histogram; its last block advances the split points), labels (1).  With the
+    curve-order permutation requested the sorted path runs instead: bounds, keys, 8 radix passes x
+    (histogram + 3 scan kernels + scatter), assignment."""
+    return 1 + 1 + 6 + 1
 
 
 def sfc_partition_labels(pos: torch.Tensor, weights: Optional[torch.Tensor], W: int, curve_type: int = 0,

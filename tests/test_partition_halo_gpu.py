@@ -76,6 +76,32 @@ def test_labels_match_oracle_weighted(cuda, W):
     assert cost.max() <= 1.2 * cost.mean()
 
 
+@pytest.mark.parametrize("curve", [0, 1])
+@pytest.mark.parametrize("W", [2, 7, 8, 64, 300, 1025])
+def test_labels_by_selection_equal_sorted_path(cuda, curve, W):
+    """Labels alone come from a digit-by-digit selection of the split points, labels + permutation from
+    the stable radix sort: both must agree with each other and with the oracle, including ties (repeated
+    positions, ordered by atom index), zero weights, weights heavy enough to cross several thresholds,
+    and more labels than atoms.  W = 1025 exceeds the selection's limit and takes the sorted path."""
+    rng = np.random.default_rng(7000 + W + curve)
+    n = 5003
+    pos = (rng.random((n, 3)) * 20.0).astype(np.float32)
+    pos[100:400] = pos[50]            # 300 atoms on one point: equal keys
+    pos[1000:1100] = pos[1000:1100].round(0)  # many coincident lattice points
+    tp = torch.as_tensor(pos, device=cuda)
+    for w in (None, rng.integers(0, 5, n).astype(np.int64), np.where(rng.random(n) < 0.01, 10_000, 0).astype(np.int64)):
+        tw = None if w is None else torch.as_tensor(w, device=cuda)
+        by_select = D.sfc_partition_labels(tp, tw, W, curve)
+        by_sort, _ = D.sfc_partition_labels(tp, tw, W, curve, return_perm=True)
+        assert torch.equal(by_select, by_sort)
+        np.testing.assert_array_equal(by_select.cpu().numpy(), O.sfc_partition(pos, w, W, curve))
+    # fewer atoms than labels, and all-zero weights
+    few = tp[:5].contiguous()
+    assert torch.equal(D.sfc_partition_labels(few, None, W, curve), D.sfc_partition_labels(few, None, W, curve, return_perm=True)[0])
+    zw = torch.zeros(n, dtype=torch.int64, device=cuda)
+    assert torch.equal(D.sfc_partition_labels(tp, zw, W, curve), D.sfc_partition_labels(tp, zw, W, curve, return_perm=True)[0])
+
+
 def test_partitioner_invariants(cuda):
     rng = np.random.default_rng(1)
     pos = (rng.random((10_000, 3)) * 40.0).astype(np.float32)
