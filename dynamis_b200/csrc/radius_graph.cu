@@ -994,11 +994,22 @@ rg_fillmask_kernel(const PairParams<T>* __restrict__ params_dev, long long* __re
         __syncwarp();
         runs_compact(delta, run_a, run_off, run_len, lt);
         int rank_base = runs_flags(flags, run_off, run_len, lane, 0);
-        for (int j = lane, sw = 0; sw < nslots; j += 32, sw++) {
-            const uint32_t word = flags[sw];
-            const int r = rank_base + __popc(word & le) - 1;
-            rank_base += __popc(word);
-            if (j < L) meta[j] = p.smeta[delta[r] + j];
+        // four slots at a time: the four gathers are in flight together before the first is stored
+        for (int sw0 = 0; sw0 < nslots; sw0 += 4) {
+            uint2 mv[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int sw = sw0 + u, j = sw * 32 + lane;
+                const uint32_t word = (sw < nslots) ? flags[sw] : 0u;
+                const int r = rank_base + __popc(word & le) - 1;
+                rank_base += __popc(word);
+                mv[u] = (j < L) ? p.smeta[delta[r] + j] : make_uint2(0u, 0u);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int j = (sw0 + u) * 32 + lane;
+                if (j < L) meta[j] = mv[u];
+            }
         }
         __syncwarp();
 
