@@ -7,6 +7,7 @@ own Python-facing names.  The compute lives in ``libdynb.so`` (hand-written CUDA
 
 from .graph import (  # noqa: F401
     launches_per_graph,
+    owned_graph,
     plan_radius_graph,
     radius_graph_pbc,
     radius_graph_pbc_counts_ex,

@@ -623,6 +623,28 @@ struct HaloArgs {
 
 constexpr int RG_MASK_SLOTS = 16;  // hit bits kept per lane and target (candidate lists up to 512 records)
 
+// Optional extras of the edge writers for the model-side glue: the shifts written with the caller's sign
+// and the Cartesian shift of every edge, unit_shift @ cell, rounded like a K = 3 float GEMM
+// (products and sums of torch.matmul(unit_shifts, cell): fma(u2, c2, fma(u1, c1, u0 * c0))).
+struct GlueArgs {
+    float* cart;  // [E,3] or nullptr
+    int negate;   // 1: write -shift
+    float c[9];   // cell, row-major
+};
+__device__ __forceinline__ void glue_write(const GlueArgs& g, float* __restrict__ shifts, long long e, int ix, int iy, int iz)
+{
+    if (g.negate) { ix = -ix; iy = -iy; iz = -iz; }
+    const float u0 = (float)ix, u1 = (float)iy, u2 = (float)iz;
+    shifts[3 * e + 0] = u0;
+    shifts[3 * e + 1] = u1;
+    shifts[3 * e + 2] = u2;
+    if (g.cart != nullptr) {
+#pragma unroll
+        for (int k = 0; k < 3; k++)
+            g.cart[3 * e + k] = __fmaf_rn(u2, g.c[6 + k], __fmaf_rn(u1, g.c[3 + k], __fmul_rn(u0, g.c[k])));
+    }
+}
+
 template <typename T> struct PairParams {
     DevHeader* h;
     const uint32_t* cstart;
@@ -645,7 +667,7 @@ constexpr int64_t RG_HEADER_BYTES = 1024;
 template <typename T, int MODE>
 __global__ void __launch_bounds__(PAIR_THREADS, 4)
 rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restrict__ ei, float* __restrict__ shifts,
-               T* __restrict__ d2out, const long long E, const HaloArgs halo, const int skip_if_masks)
+               T* __restrict__ d2out, const long long E, const HaloArgs halo, const int skip_if_masks, const GlueArgs glue)
 {
     const PairParams<T> p = *params_dev;
     extern __shared__ __align__(32) unsigned char smem_raw[];
@@ -859,9 +881,8 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                                         const long long e = bX + i;
                                         ei[e] = (long long)real_to_bits(ch.w);
                                         ei[E + e] = (long long)tm.x;
-                                        shifts[3 * e + 0] = (float)((int)(code & 1023u) - 512 + tm.y);
-                                        shifts[3 * e + 1] = (float)((int)((code >> 10) & 1023u) - 512 + tm.z);
-                                        shifts[3 * e + 2] = (float)((int)((code >> 20) & 1023u) - 512 + tm.w);
+                                        glue_write(glue, shifts, e, (int)(code & 1023u) - 512 + tm.y, (int)((code >> 10) & 1023u) - 512 + tm.z,
+                                                   (int)((code >> 20) & 1023u) - 512 + tm.w);
                                         if (d2out != nullptr) {
                                             const T tx = sel ? bx : ax, ty = sel ? by : ay, tz = sel ? bz : az;
                                             const T hx = ch.x, hy = ch.y, hz = ch.z;
@@ -910,10 +931,10 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
 constexpr int FM_META = RG_MASK_SLOTS * 32;                       // staged candidate records per warp
 constexpr int FM_WARP_BYTES = FM_META * 8 + FM_META * 2 + RUN_INDEX_BYTES;    // records + one parked slot per possible hit
 
-template <typename T>
+template <typename T, bool GLUE>
 __global__ void __launch_bounds__(PAIR_THREADS, 4)
 rg_fillmask_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restrict__ ei, float* __restrict__ shifts,
-                   const long long E)
+                   const long long E, const GlueArgs glue)
 {
     const PairParams<T> p = *params_dev;
     extern __shared__ __align__(32) unsigned char smem_raw[];
@@ -1043,9 +1064,13 @@ rg_fillmask_kernel(const PairParams<T>* __restrict__ params_dev, long long* __re
                 const long long e = base + i;
                 ei[e] = (long long)m.x;
                 ei[E + e] = (long long)tm.x;
-                shifts[3 * e + 0] = (float)((int)(code & 1023u) + sx);
-                shifts[3 * e + 1] = (float)((int)((code >> 10) & 1023u) + sy);
-                shifts[3 * e + 2] = (float)((int)((code >> 20) & 1023u) + sz);
+                if (GLUE) {
+                    glue_write(glue, shifts, e, (int)(code & 1023u) + sx, (int)((code >> 10) & 1023u) + sy, (int)((code >> 20) & 1023u) + sz);
+                } else {
+                    shifts[3 * e + 0] = (float)((int)(code & 1023u) + sx);
+                    shifts[3 * e + 1] = (float)((int)((code >> 10) & 1023u) + sy);
+                    shifts[3 * e + 2] = (float)((int)((code >> 20) & 1023u) + sz);
+                }
             }
         }
     }
@@ -1310,7 +1335,7 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
     const int smem = PAIR_WARPS * PAIR_WARP_BYTES;
     DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_COUNT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int grid = sm_count_cached() * 4 * pair_grid_waves();
-    rg_pair_kernel<T, MODE_COUNT><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, nullptr, nullptr, nullptr, 0, HaloArgs{}, 0);
+    rg_pair_kernel<T, MODE_COUNT><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, nullptr, nullptr, nullptr, 0, HaloArgs{}, 0, GlueArgs{});
     rg_post_count_kernel<T><<<(unsigned)((Nt + 255) / 256), 256, 0, stream>>>(Nt, tpos, tcount, counts_out, h);
     DYNB_CUDA_OK((exclusive_scan<uint32_t, long long>(tcount, toffset, nullptr, Nt + 1, sums64,
                                                        reinterpret_cast<long long*>(&h->E), stream)));
@@ -1321,26 +1346,33 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
 }
 
 template <typename T>
-static int rg_fill(const void* ws, int64_t* ei, float* shifts, void* d2out, int64_t E, cudaStream_t stream)
+static int rg_fill(const void* ws, int64_t* ei, float* shifts, void* d2out, int64_t E, const GlueArgs* glue_opt, cudaStream_t stream)
 {
     const unsigned char* w = static_cast<const unsigned char*>(ws);
     const auto* params_dev = reinterpret_cast<const PairParams<T>*>(w + RG_PARAMS_OFFSET);
     const int smem = PAIR_WARPS * PAIR_WARP_BYTES;
     DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_FILL>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int grid = sm_count_cached() * 4 * pair_grid_waves();
+    GlueArgs glue{};
+    if (glue_opt != nullptr) glue = *glue_opt;
     // Without distances the edges can come from the hit masks of the counting pass; which of the two
     // kernels does the work is decided on the device (header word written by the counting pass), the
     // other one returns at once.
     const int use_masks = (d2out == nullptr) ? 1 : 0;
     if (use_masks) {
         const int fsmem = PAIR_WARPS * FM_WARP_BYTES;
-        DYNB_CUDA_OK(cudaFuncSetAttribute(rg_fillmask_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, fsmem));
-        rg_fillmask_kernel<T><<<grid, PAIR_THREADS, fsmem, stream>>>(params_dev, reinterpret_cast<long long*>(ei), shifts, (long long)E);
+        if (glue_opt != nullptr) {
+            DYNB_CUDA_OK(cudaFuncSetAttribute(rg_fillmask_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fsmem));
+            rg_fillmask_kernel<T, true><<<grid, PAIR_THREADS, fsmem, stream>>>(params_dev, reinterpret_cast<long long*>(ei), shifts, (long long)E, glue);
+        } else {
+            DYNB_CUDA_OK(cudaFuncSetAttribute(rg_fillmask_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fsmem));
+            rg_fillmask_kernel<T, false><<<grid, PAIR_THREADS, fsmem, stream>>>(params_dev, reinterpret_cast<long long*>(ei), shifts, (long long)E, glue);
+        }
     }
     // behind the bit-driven writer this launch is idle in all but unusual inputs: two waves keep its cost low
     const int fgrid = use_masks ? sm_count_cached() * 4 * std::min(2, pair_grid_waves()) : grid;
     rg_pair_kernel<T, MODE_FILL><<<fgrid, PAIR_THREADS, smem, stream>>>(
-        params_dev, reinterpret_cast<long long*>(ei), shifts, static_cast<T*>(d2out), (long long)E, HaloArgs{}, use_masks);
+        params_dev, reinterpret_cast<long long*>(ei), shifts, static_cast<T*>(d2out), (long long)E, HaloArgs{}, use_masks, glue);
     DYNB_CUDA_OK(cudaGetLastError());
     return DYNB_OK;
 }
@@ -1353,7 +1385,7 @@ static int rg_halo_mark(const void* ws, const HaloArgs& ha, cudaStream_t stream)
     const int smem = PAIR_WARPS * PAIR_WARP_BYTES;
     DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_HALO>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int grid = sm_count_cached() * 4 * pair_grid_waves();
-    rg_pair_kernel<T, MODE_HALO><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, nullptr, nullptr, nullptr, 0, ha, 0);
+    rg_pair_kernel<T, MODE_HALO><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, nullptr, nullptr, nullptr, 0, ha, 0, GlueArgs{});
     DYNB_CUDA_OK(cudaGetLastError());
     return DYNB_OK;
 }
@@ -1416,8 +1448,27 @@ extern "C" int dynb_rg_fill(const void* workspace_dev, int dtype, int64_t* edge_
     if (E == 0) return DYNB_OK;
     if (edge_index_dev == nullptr || cell_shifts_dev == nullptr) return fail_arg("null output pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == DYNB_F32) return rg_fill<float>(workspace_dev, edge_index_dev, cell_shifts_dev, dist_sq_dev, E, s);
-    if (dtype == DYNB_F64) return rg_fill<double>(workspace_dev, edge_index_dev, cell_shifts_dev, dist_sq_dev, E, s);
+    if (dtype == DYNB_F32) return rg_fill<float>(workspace_dev, edge_index_dev, cell_shifts_dev, dist_sq_dev, E, nullptr, s);
+    if (dtype == DYNB_F64) return rg_fill<double>(workspace_dev, edge_index_dev, cell_shifts_dev, dist_sq_dev, E, nullptr, s);
+    return fail_arg("dtype must be DYNB_F32 or DYNB_F64");
+}
+
+extern "C" int dynb_rg_fill_glue(const void* workspace_dev, int dtype, int64_t* edge_index_dev, float* unit_shifts_dev,
+                                 float* cart_shifts_dev, const float* cell_host, int negate_shifts, int64_t E, void* stream)
+{
+    if (workspace_dev == nullptr) return fail_arg("null workspace");
+    if (E < 0) return fail_arg("E must be non-negative");
+    if (negate_shifts != 0 && negate_shifts != 1) return fail_arg("negate_shifts must be 0 or 1");
+    if (cart_shifts_dev != nullptr && cell_host == nullptr) return fail_arg("cell_host is required with cart_shifts_dev");
+    if (E == 0) return DYNB_OK;
+    if (edge_index_dev == nullptr || unit_shifts_dev == nullptr) return fail_arg("null output pointer");
+    GlueArgs g{};
+    g.cart = cart_shifts_dev;
+    g.negate = negate_shifts;
+    for (int k = 0; k < 9; k++) g.c[k] = cell_host != nullptr ? cell_host[k] : 0.0f;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == DYNB_F32) return rg_fill<float>(workspace_dev, edge_index_dev, unit_shifts_dev, nullptr, E, &g, s);
+    if (dtype == DYNB_F64) return rg_fill<double>(workspace_dev, edge_index_dev, unit_shifts_dev, nullptr, E, &g, s);
     return fail_arg("dtype must be DYNB_F32 or DYNB_F64");
 }
 

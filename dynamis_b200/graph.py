@@ -107,6 +107,24 @@ class RadiusGraphPlan:
                    "rg_fill")
 
 
+    def fill_glue(self, cell: torch.Tensor, negate_shifts: bool = True, cartesian: bool = True):
+        """Edge list with the shifts in the caller's sign and, optionally, the Cartesian shifts
+        ``unit_shifts @ cell`` (float32), written by the edge writer itself."""
+        dev = self.device
+        E = self.E
+        with torch.cuda.device(dev):
+            edge_index = torch.empty((2, E), dtype=torch.int64, device=dev)
+            unit = torch.empty((E, 3), dtype=torch.float32, device=dev)
+            cart = torch.empty((E, 3), dtype=torch.float32, device=dev) if cartesian else None
+            if E:
+                cell_h = np.ascontiguousarray(cell.detach().to("cpu").reshape(3, 3).numpy().astype(np.float32))
+                stream = torch.cuda.current_stream(dev)
+                _lib.check(_lib.lib().dynb_rg_fill_glue(self.ws.data_ptr(), self.dtype_code, edge_index.data_ptr(), unit.data_ptr(),
+                                                        cart.data_ptr() if cart is not None else None, cell_h.ctypes.data,
+                                                        1 if negate_shifts else 0, E, stream.cuda_stream), "rg_fill_glue")
+        return edge_index, unit, cart
+
+
 def plan_radius_graph(pos, cell, pbc, radius, target_indices=None) -> RadiusGraphPlan:
     """Counting phase (wrap, periodic images, cell binning, degrees, offsets).  Synchronises the
     current stream once to learn the number of edges.  ``pos`` must be non-empty."""
@@ -262,6 +280,33 @@ def radius_graph_pbc_cuda(data, radius: float, max_num_neighbors_threshold: int,
         nns.append(nn)
         off += n
     return torch.cat(eis, dim=1), torch.cat(cos, dim=0), torch.cat(nns, dim=0)
+
+
+def owned_graph(positions: torch.Tensor, cell: torch.Tensor, pbc: torch.Tensor, cutoff: float, num_local: int,
+                negate_shifts: bool = True, cartesian: bool = True):
+    """Graph a model builds over [owned | ghost] positions, in one pass.
+
+    The reference models call the radius graph on all exchanged positions and then, in three more passes
+    over the edge list, negate the offsets, keep the edges whose destination is an owned atom
+    (``edge_index[1] < num_local``) and multiply the unit shifts by the cell
+    (dynamis_model/src/dynamis_model/nnp/mace.py:591-608 ``_radius_graph`` / ``_build_owned_graph``,
+    uma.py:915-948).  Here the owned destinations are the plan's target subset, and the sign and the
+    Cartesian shifts are written by the edge writer.  Returns ``(edge_index [2, E] int64,
+    unit_shifts [E, 3] float32, shifts [E, 3] float32 or None)``."""
+    pos = positions.contiguous()
+    n = pos.size(0)
+    num_local = int(num_local)
+    if num_local < 0 or num_local > n:
+        raise RuntimeError(f"num_local must lie in [0, {n}], got {num_local}")
+    _validate(pos, cell.reshape(3, 3), pbc.reshape(-1), cutoff, 0, None)
+    dev = pos.device
+    if n == 0 or num_local == 0:
+        e = torch.empty((2, 0), dtype=torch.int64, device=dev)
+        z = torch.empty((0, 3), dtype=torch.float32, device=dev)
+        return e, z, (z.clone() if cartesian else None)
+    targets = None if num_local == n else torch.arange(num_local, dtype=torch.int64, device=dev)
+    plan = plan_radius_graph(pos, cell.reshape(3, 3), pbc.reshape(-1), cutoff, targets)
+    return plan.fill_glue(cell, negate_shifts, cartesian)
 
 
 def launches_per_graph() -> int:

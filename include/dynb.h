@@ -86,6 +86,17 @@ int dynb_rg_plan(const void* pos_dev, int dtype, int64_t n_atoms, const void* ce
 int dynb_rg_fill(const void* workspace_dev, int dtype, int64_t* edge_index_dev /* [2,E] */,
                  float* cell_shifts_dev /* [E,3] */, void* dist_sq_dev /* [E] or NULL */, int64_t E, void* stream);
 
+/* dynb_rg_fill for the model-side graph glue (dynamis_model/src/dynamis_model/nnp/mace.py:591-608,
+ * uma.py:915-948): the models negate the offsets (unit_shifts = -cell_offsets), keep the edges whose
+ * destination is an owned atom (edge_index[1] < num_local) and form shifts = unit_shifts @ cell in
+ * float32 — three more passes over the edge list.  Here the owned-destination filter is the plan's
+ * target subset 0..num_local-1, negate_shifts = 1 writes the offsets negated, and cart_shifts_dev
+ * (optional, may be NULL) receives unit_shifts @ cell_host (9 floats, row-major) with the rounding of
+ * a K = 3 float32 GEMM. */
+int dynb_rg_fill_glue(const void* workspace_dev, int dtype, int64_t* edge_index_dev /* [2,E] */,
+                      float* unit_shifts_dev /* [E,3] */, float* cart_shifts_dev /* [E,3] or NULL */,
+                      const float* cell_host /* [9] */, int negate_shifts, int64_t E, void* stream);
+
 /* Halo marking over a plan (all atoms as targets, radius = cutoff + ghost buffer): for every edge
  * src -> dst whose endpoints have different owners, sets bit owner[dst] of
  * needed_dev[src * words + ...] (words = ceil(world_size / 32)) and has_foreign_dev[dst] = 1.
