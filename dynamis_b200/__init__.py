@@ -41,3 +41,5 @@ from .state import (  # noqa: F401
     PartitionMessagePassingInfo,
     SimulationConfig,
 )
+
+from . import integrators  # noqa: F401,E402

@@ -245,6 +245,20 @@ int dynb_scatter_rows(const void* rows_dev, int64_t row_bytes, const int64_t* id
 int dynb_drift_flag(const float* cur_dev, const float* ref_dev, const float* vel_dev, float* prev_vel_dev, int64_t n,
                     double dt, double threshold, uint32_t* state_dev, int32_t* flag_dev, void* stream);
 
+/* ------------------------------------------------------------------ integrator steps
+ * Replaces EulerIntegrator::step, VerletIntegrator::halfstep1/2 and LangevinIntegrator::halfstep1/2
+ * (dynamis_integrator/src/csrc/euler_integrator.cu:9-75, verlet_integrator.cu:9-116,
+ * langevin_integrator.cu:9-150), same per-component arithmetic in float32, in place.
+ * kind: 0 Euler step, 1 / 2 Verlet half-steps, 3 / 4 Langevin half-steps (noise_dev, gamma, kT used by
+ * 3 and 4 only; pos_dev is not touched by 2 and 4).
+ * With drift_flag_dev != NULL (kinds 0, 1, 3) the same launch also produces the drift word of
+ * dynb_drift_flag from the new positions and velocities (drift_ref_dev, drift_prev_vel_dev,
+ * drift_threshold, drift_state_dev as there), instead of a second pass over the state. */
+int dynb_integrator_step(int kind, float* pos_dev, float* vel_dev, const float* frc_dev, const float* mass_dev,
+                         const float* noise_dev, int64_t n_atoms, double dt, double gamma, double kT,
+                         const float* drift_ref_dev, float* drift_prev_vel_dev, double drift_threshold,
+                         uint32_t* drift_state_dev, int32_t* drift_flag_dev, void* stream);
+
 /* ------------------------------------------------------------------ partition without a workspace
  * No counterpart in the reference.  Same result as dynb_sfc_partition, for callers that must not
  * allocate device memory while they run (an engine that gave its whole memory budget to its own

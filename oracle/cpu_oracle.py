@@ -44,7 +44,7 @@ class _OrcGraph(ctypes.Structure):
 def build(force: bool = False) -> str:
     """Compile liborc.so with the Makefile next to this file (gcc, a few seconds)."""
     so = os.path.join(_HERE, "liborc.so")
-    srcs = [os.path.join(_HERE, f) for f in ("rg_oracle.c", "rg_oracle_impl.h", "Makefile")]
+    srcs = [os.path.join(_HERE, f) for f in ("rg_oracle.c", "rg_oracle_impl.h", "integrator_oracle.c", "Makefile")]
     if force or not os.path.exists(so) or any(os.path.getmtime(s) > os.path.getmtime(so) for s in srcs):
         subprocess.run(["make", "-C", _HERE, "-s", "liborc.so"], check=True)
     return so
@@ -70,8 +70,28 @@ def lib():
         L.orc_geometry_f32.restype = None
         L.orc_edge_keep_mask_f32.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_float, ctypes.c_int64, ctypes.c_void_p]
         L.orc_edge_keep_mask_f32.restype = None
+        L.orc_integrator_step.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 5 + [ctypes.c_int64] + [ctypes.c_float] * 3
+        L.orc_integrator_step.restype = None
+        L.orc_drift_flag.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int64, ctypes.c_float, ctypes.c_float]
+        L.orc_drift_flag.restype = ctypes.c_int
         _LIB = L
     return _LIB
+
+
+def integrator_step(kind, pos, vel, frc, mass, noise, dt, gamma=0.0, kT=0.0):
+    """In-place integrator step on float32 numpy arrays (integrator_oracle.c).  kind: 0 Euler, 1/2 Verlet
+    half-steps, 3/4 Langevin half-steps; ``pos`` may be None for 2 and 4, ``noise`` for 0-2."""
+    p = (lambda a: a.ctypes.data if a is not None else None)
+    for a in (pos, vel, frc, mass, noise):
+        assert a is None or (a.dtype == np.float32 and a.flags.c_contiguous)
+    lib().orc_integrator_step(int(kind), p(pos), p(vel), p(frc), p(mass), p(noise), vel.shape[0], dt, gamma, kT)
+
+
+def drift_flag(cur, ref, vel, prev_vel, dt, threshold) -> int:
+    """2-bit drift word (simulatorState.py:257-293); prev_vel is overwritten with vel."""
+    for a in (cur, ref, vel, prev_vel):
+        assert a.dtype == np.float32 and a.flags.c_contiguous
+    return int(lib().orc_drift_flag(cur.ctypes.data, ref.ctypes.data, vel.ctypes.data, prev_vel.ctypes.data, cur.shape[0], dt, threshold))
 
 
 def max_threads() -> int:

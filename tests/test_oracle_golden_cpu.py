@@ -125,3 +125,31 @@ def test_send_recv_symmetry():
         ghosts = out[r][m["num_local"]:, 0]
         owner = (ghosts // 100000).astype(int)
         assert (owner == pid[m["recv_atom_global"]]).all()
+
+
+def test_integrator_oracle_analytic_cases():
+    """The closed-form cases of the reference's integrator tests (dynamis_integrator/tests/test_verlet.py,
+    test_euler.py): the oracle must reproduce them before the CUDA kernels are compared with it."""
+    f32 = lambda rows: np.array(rows, dtype=np.float32)
+    pos, vel, frc, mass = f32([[0, 0, 0]]), f32([[0, 0, 0]]), f32([[2, 0, 0]]), f32([1])
+    O.integrator_step(1, pos, vel, frc, mass, None, 0.5)
+    np.testing.assert_allclose(vel, [[0.5, 0, 0]]); np.testing.assert_allclose(pos, [[0.25, 0, 0]])
+    O.integrator_step(2, None, vel, frc, mass, None, 0.5)
+    np.testing.assert_allclose(vel, [[1.0, 0, 0]])
+    pos, vel, frc, mass = f32([[0, 0, 0]]), f32([[0, 0, 0]]), f32([[4, 0, 0]]), f32([2])
+    O.integrator_step(0, pos, vel, frc, mass, None, 0.25)
+    np.testing.assert_allclose(vel, [[0.5, 0, 0]]); np.testing.assert_allclose(pos, [[0.125, 0, 0]])
+    # Langevin, gamma = 0: the noise drops out and the half-steps are Verlet's
+    rng = np.random.default_rng(3)
+    p, v, f = (rng.normal(size=(50, 3)).astype(np.float32) for _ in range(3))
+    m = (rng.random(50) + 1).astype(np.float32); nz = rng.normal(size=(50, 3)).astype(np.float32)
+    p2, v2 = p.copy(), v.copy()
+    O.integrator_step(3, p, v, f, m, nz, 0.5, 0.0, 0.0257)
+    O.integrator_step(1, p2, v2, f, m, None, 0.5)
+    np.testing.assert_allclose(p, p2, rtol=1e-6); np.testing.assert_allclose(v, v2, rtol=1e-6)
+    # drift word: bit 0 reach >= threshold, bit 1 displacement > threshold
+    cur, ref = f32([[1, 0, 0], [0, 0, 0]]), f32([[0, 0, 0], [0, 0, 0]])
+    vv, pv = f32([[0, 0, 0], [0, 0, 0]]), f32([[0, 0, 0], [0, 0, 0]])
+    assert O.drift_flag(cur, ref, vv, pv.copy(), 0.5, 2.0) == 0
+    assert O.drift_flag(cur, ref, vv, pv.copy(), 0.5, 1.0) == 1
+    assert O.drift_flag(cur, ref, vv, pv.copy(), 0.5, 0.5) == 3
