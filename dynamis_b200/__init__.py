@@ -26,9 +26,11 @@ from .exchange import (  # noqa: F401
 )
 from .halo import extract_halo_info, filter_edges_to_radius  # noqa: F401
 from .partition import (  # noqa: F401
+    KDTreePartitioner,
     SFCCurveType,
     SFCPartitioner,
     SimpleSpatialPartitioner,
+    kdtree_partition_labels,
     launches_per_partition,
     sfc_keys,
     sfc_partition_labels,

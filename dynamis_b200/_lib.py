@@ -81,6 +81,8 @@ SIGNATURES = {
     "dynb_copy_async": (_i32, [_p, _p, _i64, _p]),
     "dynb_scatter_rows": (_i32, [_p, _i64, _p, _i64, _i64, _p, _p, _p]),
     "dynb_drift_flag": (_i32, [_p, _p, _p, _p, _i64, _f64, _f64, _p, _p, _p]),
+    "dynb_kdtree_workspace_bytes": (_i32, [_i64, _i64, ctypes.POINTER(_i64)]),
+    "dynb_kdtree_partition": (_i32, [_p, _i64, _p, _i64, _p, _p, _i64, _p]),
     "dynb_integrator_step": (_i32, [_i32, _p, _p, _p, _p, _p, _i64, _f64, _f64, _f64, _p, _p, _f64, _p, _p, _p]),
     "dynb_sfc_static_max_atoms": (_i64, []),
     "dynb_sfc_partition_static": (_i32, [_p, _i64, _p, _i64, _i32, _p, _p, _p]),

@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 SO = os.path.join(HERE, "libdynb.so")
-SOURCES = ["lib.cu", "radius_graph.cu", "sfc.cu", "halo.cu", "exchange.cu", "state_ops.cu", "integrators.cu"]
+SOURCES = ["lib.cu", "radius_graph.cu", "sfc.cu", "halo.cu", "exchange.cu", "state_ops.cu", "integrators.cu", "kdtree.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -245,6 +245,60 @@ class SFCPartitioner(AbstractPartitioner):
         return info
 
 
+def kdtree_partition_labels(pos: torch.Tensor, weights: Optional[torch.Tensor], W: int) -> torch.Tensor:
+    """Rank label in [0, W) per atom by recursive bisection along the widest axis
+    (reference: kdtree_bisect_cuda, partition/kdtree.cpp:9-26)."""
+    if not pos.is_cuda:
+        raise RuntimeError("pos must be a CUDA tensor")
+    if pos.dim() != 2 or pos.size(1) != 3:
+        raise RuntimeError(f"pos must have shape [N, 3], got [{pos.size(0)}, {pos.size(1) if pos.dim() > 1 else ''}]")
+    if pos.dtype != torch.float32:
+        raise RuntimeError(f"pos must be float32, got {pos.dtype}")
+    if W < 1:
+        raise RuntimeError(f"W must be >= 1, got {W}")
+    pos = pos.contiguous()
+    N, dev = pos.size(0), pos.device
+    if weights is not None:
+        if not weights.is_cuda:
+            raise RuntimeError("weights must be a CUDA tensor")
+        if weights.dim() != 1 or weights.size(0) != N:
+            raise RuntimeError(f"weights must have shape [N], got [{weights.size(0)}]")
+        weights = weights.to(torch.int64).contiguous()
+    L = _lib.lib()
+    with torch.cuda.device(dev):
+        labels = torch.empty((N,), dtype=torch.int64, device=dev)
+        if N > 0:
+            nbytes = ctypes.c_int64()
+            _lib.check(L.dynb_kdtree_workspace_bytes(N, int(W), ctypes.byref(nbytes)), "kdtree_workspace_bytes")
+            ws = scratch(dev, "kdtree", nbytes.value)
+            _lib.check(L.dynb_kdtree_partition(pos.data_ptr(), N, weights.data_ptr() if weights is not None else None, int(W),
+                                               labels.data_ptr(), ws.data_ptr(), ws.numel(), _stream(dev)), "kdtree_partition")
+    return labels
+
+
+class KDTreePartitioner(AbstractPartitioner):
+    """Recursive bisection along the widest axis into world_size parts of equal count, or of equal
+    summed ``edge_counts``; with a SimulationConfig the weights are the in-degrees at the cutoff and the
+    graph is kept (reference: partition/kdtree_partitioner.cpp:52-164)."""
+
+    def partition(self, state: MolecularInfo, env: DistEnvironment, config: Optional[SimulationConfig] = None):
+        pos = state.atom_positions
+        if not pos.is_cuda:
+            raise RuntimeError("KDTreePartitioner: atom_positions must be a CUDA tensor (this build has no CPU path)")
+        W = int(env.world_size)
+        pos32 = pos.to(torch.float32)
+        if config is None:
+            labels = kdtree_partition_labels(pos32, state.edge_counts, W)
+            return _finish_partition(labels, state, env)
+        cutoff = float(torch.tensor(config.cutoff, dtype=torch.float32).item())
+        cell = config.cell.to(torch.float32)
+        ei, _, _, counts = radius_graph_pbc_ex(pos32, cell, config.pbc.to(torch.bool), cutoff, PARTITION_MAX_NUM_NEIGHBORS, False)
+        labels = kdtree_partition_labels(pos32, counts.to(torch.int64), W)
+        info = _finish_partition(labels, state, env)
+        info.edge_index = ei
+        return info
+
+
 class SimpleSpatialPartitioner(AbstractPartitioner):
     """Contiguous index split: rank r owns atoms [r*(N//W), (r+1)*(N//W)), the last rank the
     remainder (reference: partition/simple_spatial_partitioner.cpp:6-47)."""

@@ -245,6 +245,16 @@ int dynb_scatter_rows(const void* rows_dev, int64_t row_bytes, const int64_t* id
 int dynb_drift_flag(const float* cur_dev, const float* ref_dev, const float* vel_dev, float* prev_vel_dev, int64_t n,
                     double dt, double threshold, uint32_t* state_dev, int32_t* flag_dev, void* stream);
 
+/* ------------------------------------------------------------------ KD-tree partition
+ * Replaces kdtree_bisect_cuda (dynamis_state/src/csrc/partition/kdtree.cpp:9-26,
+ * kdtree_kernels.cu:264-467): labels_dev[i] in [0, W) by recursive bisection along the widest axis of
+ * each segment, ceil(log2 W) levels.  weights_dev: int64 per-atom cost (non-negative) or NULL (equal
+ * counts).  Atoms with equal coordinates are ordered by ascending index; weights are summed exactly
+ * (the reference uses a float32 cumulative sum, identical while the sums stay below 2^24). */
+int dynb_kdtree_workspace_bytes(int64_t n_atoms, int64_t W, int64_t* bytes);
+int dynb_kdtree_partition(const float* pos_dev, int64_t n_atoms, const int64_t* weights_dev, int64_t W,
+                          int64_t* labels_dev, void* workspace_dev, int64_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------ integrator steps
  * Replaces EulerIntegrator::step, VerletIntegrator::halfstep1/2 and LangevinIntegrator::halfstep1/2
  * (dynamis_integrator/src/csrc/euler_integrator.cu:9-75, verlet_integrator.cu:9-116,

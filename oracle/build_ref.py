@@ -1,7 +1,7 @@
 """TEST INFRASTRUCTURE ONLY — compiles the reference's own CUDA sources for the hot path into
 oracle/_ref/libdynamis_ref.so (git-ignored), for use as the parity oracle on a GPU.
 
-The three reference .cu files are compiled where they lie (nothing is copied), with nvcc for
+The four reference .cu files are compiled where they lie (nothing is copied), with nvcc for
 compute_100 exactly as the reference's own CMake does (plain SIMT, default FMA contraction),
 against this image's libtorch headers, together with ref_shim.cpp (ours) which registers them as
 torch ops in the ``dynamis_ref`` namespace.  The reference's build system is not run.
@@ -22,6 +22,7 @@ REF_SOURCES = [
     "dynamis_state/src/csrc/graph/radius_graph_kernels.cu",
     "dynamis_state/src/csrc/partition/sfc_kernels.cu",
     "dynamis_state/src/csrc/graph/dist_graph_ops_kernels.cu",
+    "dynamis_state/src/csrc/partition/kdtree_kernels.cu",
 ]
 
 

@@ -381,3 +381,69 @@ def exchange_backward(grads, num_local, send_offsets, send_local_indices, recv_o
             np.add.at(acc, rows, grads[p][g0:g0 + rows.shape[0]].astype(np.float64))
         out.append(acc)
     return out
+
+
+def _sortable_u32(x):
+    """Order-preserving map float32 -> uint32 (kdtree_kernels.cu:9-14)."""
+    b = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    return np.where(b >> 31, ~b, b | np.uint32(0x80000000)).astype(np.uint32)
+
+
+def kdtree_partition(pos, weights, W):
+    """Labels of the recursive bisection along the widest axis, level by level as the reference's CUDA
+    driver does it (dynamis_state/src/csrc/partition/kdtree_kernels.cu:264-467; the same rule as the
+    host recursion, kdtree_partitioner.cpp:10-50): per segment the axis of largest extent (first on
+    ties), a stable sort by (segment, coordinate), the split at size // 2 (equal counts) or at the
+    first position whose inclusive prefix weight reaches half of the segment's weight, clamped to
+    [1, size - 1].  Weights are summed as exact integers (the reference's float32 cumulative sum is
+    identical while all sums stay below 2**24)."""
+    pos = np.ascontiguousarray(pos, dtype=np.float32)
+    n = pos.shape[0]
+    if W == 1 or n == 0:
+        return np.zeros(n, dtype=np.int64)
+    levels = int(np.ceil(np.log2(W)))
+    parts = [int(W)]
+    seg = np.zeros(n, dtype=np.int64)
+    w = None if weights is None else np.asarray(weights, dtype=np.int64)
+    for _ in range(levels):
+        S = len(parts)
+        child_l, child_r, nxt = [], [], []
+        for p in parts:
+            if p <= 1:
+                child_l.append(len(nxt)); child_r.append(len(nxt)); nxt.append(p)
+            else:
+                child_l.append(len(nxt)); nxt.append(p // 2)
+                child_r.append(len(nxt)); nxt.append(p - p // 2)
+        coord = np.empty(n, dtype=np.float32)
+        for s in range(S):
+            m = seg == s
+            if not m.any():
+                continue
+            ext = pos[m].max(axis=0) - pos[m].min(axis=0)          # float32 subtraction, as the kernel
+            axis, best = 0, np.float32(-1.0)
+            for d in range(3):
+                if ext[d] > best:
+                    best, axis = ext[d], d
+            coord[m] = pos[m, axis]
+        key = (seg.astype(np.uint64) << np.uint64(32)) | _sortable_u32(coord).astype(np.uint64)
+        order = np.argsort(key, kind="stable")
+        new_seg = np.empty(n, dtype=np.int64)
+        start = 0
+        for s in range(S):
+            sz = int((seg == s).sum())
+            idx = order[start:start + sz]
+            if parts[s] <= 1 or sz <= 1:
+                mid = sz
+            elif w is None:
+                mid = min(max(sz // 2, 1), sz - 1)
+            else:
+                cs = np.cumsum(w[idx])
+                total = int(cs[-1])
+                lo = int(np.searchsorted(2 * cs >= total, True))   # first position with 2 * cumsum >= total
+                mid = min(max(lo, 1), sz - 1)
+            new_seg[idx[:mid]] = child_l[s]
+            new_seg[idx[mid:]] = child_r[s]
+            start += sz
+        seg, parts = new_seg, nxt
+    base = np.concatenate([[0], np.cumsum(parts)[:-1]]).astype(np.int64)
+    return base[seg]

@@ -6,6 +6,7 @@
 //   dynamis_state/src/csrc/graph/radius_graph_kernels.cu      radius_graph_pbc_cuda_impl_ex
 //   dynamis_state/src/csrc/partition/sfc_kernels.cu           sfc_partition_cuda_impl
 //   dynamis_state/src/csrc/graph/dist_graph_ops_kernels.cu    filter_edges / extract_halo_info
+//   dynamis_state/src/csrc/partition/kdtree_kernels.cu        kdtree_bisect_cuda_impl
 #include <ATen/ATen.h>
 #include <torch/library.h>
 #include <tuple>
@@ -15,6 +16,7 @@ radius_graph_pbc_cuda_impl_ex(at::Tensor pos, at::Tensor cell, at::Tensor pbc, f
                               int64_t max_num_neighbors, bool enforce_max_strictly,
                               c10::optional<at::Tensor> target_indices, bool counts_only);
 at::Tensor sfc_partition_cuda_impl(at::Tensor pos, at::Tensor weights, int64_t W, int64_t curve_type);
+at::Tensor kdtree_bisect_cuda_impl(at::Tensor pos, at::Tensor weights, int64_t W);  // kdtree_kernels.cu
 std::tuple<at::Tensor, at::Tensor>
 filter_edges_to_radius_cuda_impl(at::Tensor edges, at::Tensor cell_shifts, at::Tensor pos, at::Tensor cell,
                                  double radius);
@@ -51,11 +53,20 @@ ref_extract_halo_info(at::Tensor edges, at::Tensor pid, at::Tensor mine, int64_t
     return extract_halo_info_cuda_impl(edges.contiguous(), pid.to(at::kLong).contiguous(), mine.contiguous(), rank, W, N);
 }
 
+// same argument preparation as kdtree_bisect_cuda (dynamis_state/src/csrc/partition/kdtree.cpp:9-26)
+static at::Tensor ref_kdtree_partition(at::Tensor pos, c10::optional<at::Tensor> weights, int64_t W)
+{
+    at::Tensor w;
+    if (weights.has_value() && weights->defined()) w = weights->to(at::kFloat).contiguous();
+    return kdtree_bisect_cuda_impl(pos.contiguous(), w, W);
+}
+
 TORCH_LIBRARY(dynamis_ref, m)
 {
     m.def("radius_graph(Tensor pos, Tensor cell, Tensor pbc, float radius, Tensor? target_indices, bool counts_only)"
           " -> (Tensor, Tensor, Tensor, Tensor)", &ref_radius_graph);
     m.def("sfc_partition(Tensor pos, Tensor? weights, int W, int curve) -> Tensor", &ref_sfc_partition);
+    m.def("kdtree_partition(Tensor pos, Tensor? weights, int W) -> Tensor", &ref_kdtree_partition);
     m.def("filter_edges(Tensor edges, Tensor shifts, Tensor pos, Tensor cell, float radius) -> (Tensor, Tensor)",
           &ref_filter_edges);
     m.def("extract_halo_info(Tensor edges, Tensor pid, Tensor mine, int rank, int W, int N)"
