@@ -72,6 +72,7 @@ SIGNATURES = {
     "dynb_inverse_csr_workspace_bytes": (_i32, [_i64, _i64, ctypes.POINTER(_i64)]),
     "dynb_inverse_csr": (_i32, [_p, _i64, _i64, _p, _p, _p, _p, _i64, _p]),
     "dynb_unpack_add_rows": (_i32, [_p, _i64, _i64, _i32, _p, _p, _p, _p, _p]),
+    "dynb_add_rows_listed": (_i32, [_p, _i64, _i64, _i32, _p, _p, _p, _p, _p]),
     "dynb_ipc_alloc": (_i32, [_i64, ctypes.POINTER(_p)]),
     "dynb_ipc_free": (_i32, [_p]),
     "dynb_ipc_export": (_i32, [_p, _p]),

@@ -132,6 +132,30 @@ unpack_add_rows_kernel(const V* __restrict__ grad, int64_t n_local, int64_t q, c
     }
 }
 
+// The same sum restricted to the rows that receive something: out already holds grad (copied while the
+// rows were still on their way), rows[] lists the local rows named by at least one send entry.
+template <typename T, typename V, int VW>
+__global__ void __launch_bounds__(256)
+add_rows_listed_kernel(const int64_t* __restrict__ rows, int64_t n_rows, int64_t q, const V* __restrict__ recv,
+                       const int64_t* __restrict__ inv_offsets, const uint32_t* __restrict__ inv_entries, V* __restrict__ out)
+{
+    const int64_t total = n_rows * q;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / q, col = i - r * q;
+        const int64_t row = rows[r];
+        V v = out[row * q + col];
+        const int64_t b = inv_offsets[row], e = inv_offsets[row + 1];
+        T* a = reinterpret_cast<T*>(&v);
+        for (int64_t k = b; k < e; k++) {
+            const V x = recv[(int64_t)inv_entries[k] * q + col];
+            const T* xx = reinterpret_cast<const T*>(&x);
+#pragma unroll
+            for (int c = 0; c < VW; c++) a[c] += xx[c];
+        }
+        out[row * q + col] = v;
+    }
+}
+
 __global__ void __launch_bounds__(256)
 inv_keys_kernel(const int64_t* __restrict__ send_local, int64_t total_send, int64_t n_local, uint64_t* __restrict__ keys,
                 uint32_t* __restrict__ vals, uint32_t* __restrict__ counts, uint32_t* __restrict__ bad)
@@ -297,6 +321,40 @@ extern "C" int dynb_unpack_add_rows(const void* grad_dev, int64_t n_local, int64
             unpack_add_rows_kernel<double, double, 1><<<grid_for(n_local * feature_dim), 256, 0, s>>>(
                 static_cast<const double*>(grad_dev), n_local, feature_dim, static_cast<const double*>(recv_dev), inv_offsets_dev,
                 inv_entries_dev, static_cast<double*>(out_dev));
+        }
+    }
+    DYNB_CUDA_OK(cudaGetLastError());
+    return DYNB_OK;
+}
+
+extern "C" int dynb_add_rows_listed(const int64_t* rows_dev, int64_t n_rows, int64_t feature_dim, int dtype, const void* recv_dev,
+                                    const int64_t* inv_offsets_dev, const uint32_t* inv_entries_dev, void* out_dev, void* stream)
+{
+    if (n_rows < 0 || feature_dim <= 0) return fail_arg("bad arguments");
+    if (dtype != DYNB_F32 && dtype != DYNB_F64) return fail_arg("dtype must be DYNB_F32 or DYNB_F64");
+    if (n_rows == 0) return DYNB_OK;
+    if (rows_dev == nullptr || out_dev == nullptr || inv_offsets_dev == nullptr || inv_entries_dev == nullptr || recv_dev == nullptr)
+        return fail_arg("null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int64_t row_bytes = feature_dim * (dtype == DYNB_F64 ? 8 : 4);
+    const bool al = (reinterpret_cast<uintptr_t>(out_dev) | reinterpret_cast<uintptr_t>(recv_dev)) % 16 == 0;
+    if (dtype == DYNB_F32) {
+        if (al && row_bytes % 16 == 0) {
+            const int64_t q = row_bytes / 16;
+            add_rows_listed_kernel<float, float4, 4><<<grid_for(n_rows * q), 256, 0, s>>>(
+                rows_dev, n_rows, q, static_cast<const float4*>(recv_dev), inv_offsets_dev, inv_entries_dev, static_cast<float4*>(out_dev));
+        } else {
+            add_rows_listed_kernel<float, float, 1><<<grid_for(n_rows * feature_dim), 256, 0, s>>>(
+                rows_dev, n_rows, feature_dim, static_cast<const float*>(recv_dev), inv_offsets_dev, inv_entries_dev, static_cast<float*>(out_dev));
+        }
+    } else {
+        if (al && row_bytes % 16 == 0) {
+            const int64_t q = row_bytes / 16;
+            add_rows_listed_kernel<double, double2, 2><<<grid_for(n_rows * q), 256, 0, s>>>(
+                rows_dev, n_rows, q, static_cast<const double2*>(recv_dev), inv_offsets_dev, inv_entries_dev, static_cast<double2*>(out_dev));
+        } else {
+            add_rows_listed_kernel<double, double, 1><<<grid_for(n_rows * feature_dim), 256, 0, s>>>(
+                rows_dev, n_rows, feature_dim, static_cast<const double*>(recv_dev), inv_offsets_dev, inv_entries_dev, static_cast<double*>(out_dev));
         }
     }
     DYNB_CUDA_OK(cudaGetLastError());

@@ -91,7 +91,17 @@ class _ReversePlan:
                        "inverse_csr")
             if int(bad.item()) != 0:
                 raise RuntimeError("send_local_indices contains an index outside [0, n_local)")
+            # local rows that receive at least one gradient row (for the two-step accumulation)
+            self.rows = torch.nonzero(self.inv_offsets[1:] > self.inv_offsets[:-1]).reshape(-1).contiguous()
         self.n_local = n_local
+
+    def add_received(self, recv_ptr: int, out: torch.Tensor) -> None:
+        """out (already holding the local gradient rows) += received rows, for the rows that receive any."""
+        dev = out.device
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().dynb_add_rows_listed(self.rows.data_ptr(), self.rows.numel(), out.size(1), _DT[out.dtype], recv_ptr,
+                                                       self.inv_offsets.data_ptr(), self.inv_entries.data_ptr(), out.data_ptr(),
+                                                       _stream(dev)), "add_rows_listed")
 
     def apply(self, grad: torch.Tensor, recv_ptr: int, out: torch.Tensor) -> None:
         dev = grad.device
@@ -345,9 +355,10 @@ class FeatureExchanger:
         x = local_features.contiguous()
         with torch.cuda.device(self.device):
             out = torch.empty((self.n_local + self.total_recv, self.F), dtype=self.dtype, device=self.device)
+            # rows for the peers leave first; the copy of the local rows then runs while they travel
+            gen = self._push("fwd", x, self.send_local.data_ptr(), 0, self.total_send)
             _lib.check(_lib.lib().dynb_copy_async(out.data_ptr(), x.data_ptr(), self.n_local * self.row_bytes, _stream(self.device)),
                        "copy_async")
-            gen = self._push("fwd", x, self.send_local.data_ptr(), 0, self.total_send)
         return out, gen
 
     def forward_end(self, out: torch.Tensor, gen: int) -> torch.Tensor:
@@ -370,13 +381,16 @@ class FeatureExchanger:
             raise RuntimeError(f"grad_output shape mismatch: expected [{self.n_local + self.total_recv}, {self.F}]")
         with torch.cuda.device(self.device):
             gen = self._push("bwd", g, None, self.n_local, self.total_recv)
-        return g, gen
+            # the local gradient rows are copied while the ghost rows travel; backward_end adds what arrived
+            out = torch.empty((self.n_local, self.F), dtype=self.dtype, device=self.device)
+            _lib.check(_lib.lib().dynb_copy_async(out.data_ptr(), g.data_ptr(), self.n_local * self.row_bytes, _stream(self.device)),
+                       "copy_async")
+        return out, gen
 
-    def backward_end(self, g: torch.Tensor, gen: int) -> torch.Tensor:
+    def backward_end(self, out: torch.Tensor, gen: int) -> torch.Tensor:
         with torch.cuda.device(self.device):
             self._wait("bwd", gen)
-            out = torch.empty((self.n_local, self.F), dtype=self.dtype, device=self.device)
-            self.reverse.apply(g, self._base + self.grad_off[gen & 1], out)
+            self.reverse.add_received(self._base + self.grad_off[gen & 1], out)
         return out
 
     def feature_push_backward(self, grad_output: torch.Tensor, grad_input_shape=None, partition_info=None) -> torch.Tensor:

@@ -219,6 +219,12 @@ int dynb_inverse_csr(const int64_t* send_local_dev, int64_t total_send, int64_t 
                      void* stream);
 int dynb_unpack_add_rows(const void* grad_dev, int64_t n_local, int64_t feature_dim, int dtype, const void* recv_dev,
                          const int64_t* inv_offsets_dev, const uint32_t* inv_entries_dev, void* out_dev, void* stream);
+/* The same accumulation in two steps, so that the copy of the local gradient rows can run while the
+ * peers' rows are still arriving: the caller copies grad[0:n_local] into out_dev, waits for the rows, and
+ * this call adds the received rows to the n_rows local rows listed in rows_dev (those named by at least
+ * one send entry), in the same order as dynb_unpack_add_rows — the result is bit-identical. */
+int dynb_add_rows_listed(const int64_t* rows_dev, int64_t n_rows, int64_t feature_dim, int dtype, const void* recv_dev,
+                         const int64_t* inv_offsets_dev, const uint32_t* inv_entries_dev, void* out_dev, void* stream);
 
 /* Peer-visible memory (allocate_ipc_buffer / export_ipc_handle / cudaIpcOpenMemHandle,
  * dynamis_model/src/csrc/exchange/ipc_exchanger.cpp:117-252, 406-430).  These are the only calls of
