@@ -112,15 +112,7 @@ __device__ __forceinline__ void image_pos(const Geom<T>& g, T px, T py, T pz, in
     z = pz + shift_z;
 }
 
-// flags: bit d = "may be shifted up along d", bit 3+d = "may be shifted down along d"
-__device__ __forceinline__ bool image_needed(uint32_t flags, int dx, int dy, int dz)
-{
-    bool ok = true;
-    if (dx > 0) ok = ok && (flags & 1u); else if (dx < 0) ok = ok && (flags & 8u);
-    if (dy > 0) ok = ok && (flags & 2u); else if (dy < 0) ok = ok && (flags & 16u);
-    if (dz > 0) ok = ok && (flags & 4u); else if (dz < 0) ok = ok && (flags & 32u);
-    return ok;
-}
+// image flags of an atom: bit d = "may be shifted up along d", bit 3+d = "may be shifted down along d"
 
 template <typename T>
 __device__ __forceinline__ uint32_t cell_of(const DevHeader& h, T x, T y, T z)
@@ -208,10 +200,14 @@ rg_wrap_kernel(const T* __restrict__ pos, int64_t N, Geom<T> g, int vec_ok, Vec4
             mn[2] = mx[2] = ordered_any(z);
             count = 1;
         } else if (!(status & DYNB_RG_NONFINITE)) {
-            for (int dx = -g.rep[0]; dx <= g.rep[0]; dx++)
-                for (int dy = -g.rep[1]; dy <= g.rep[1]; dy++)
-                    for (int dz = -g.rep[2]; dz <= g.rep[2]; dz++) {
-                        if (!image_needed(flags, dx, dy, dz)) continue;
+            // the images an atom needs form a box of shifts (the flags are per axis and direction): walk
+            // that box only, so that a warp runs as many rounds as its busiest atom has images, not (2 rep + 1)^3
+            const int lo0 = (flags & 8u) ? -g.rep[0] : 0, hi0 = (flags & 1u) ? g.rep[0] : 0;
+            const int lo1 = (flags & 16u) ? -g.rep[1] : 0, hi1 = (flags & 2u) ? g.rep[1] : 0;
+            const int lo2 = (flags & 32u) ? -g.rep[2] : 0, hi2 = (flags & 4u) ? g.rep[2] : 0;
+            for (int dx = lo0; dx <= hi0; dx++)
+                for (int dy = lo1; dy <= hi1; dy++)
+                    for (int dz = lo2; dz <= hi2; dz++) {
                         T x, y, z;
                         image_pos(g, wx, wy, wz, dx, dy, dz, x, y, z);
                         unsigned long long ox = ordered_any(x), oy = ordered_any(y), oz = ordered_any(z);
@@ -468,11 +464,13 @@ rg_bin_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ targets, Geom<T
         const uint32_t flags = (uint32_t)real_to_bits(w.w);
         const int k1 = 2 * g.rep[1] + 1, k2 = 2 * g.rep[2] + 1;
         const unsigned long long K = (unsigned long long)(2 * g.rep[0] + 1) * k1 * k2;
-        const int r0 = flags ? g.rep[0] : 0, r1 = flags ? g.rep[1] : 0, r2 = flags ? g.rep[2] : 0;  // interior: own image only
-        for (int dx = -r0; dx <= r0; dx++)
-            for (int dy = -r1; dy <= r1; dy++)
-                for (int dz = -r2; dz <= r2; dz++) {
-                    if (!image_needed(flags, dx, dy, dz)) continue;
+        // box of needed shifts (see rg_wrap_kernel); same (dx, dy, dz) order as a full walk
+        const int lo0 = (flags & 8u) ? -g.rep[0] : 0, hi0 = (flags & 1u) ? g.rep[0] : 0;
+        const int lo1 = (flags & 16u) ? -g.rep[1] : 0, hi1 = (flags & 2u) ? g.rep[1] : 0;
+        const int lo2 = (flags & 32u) ? -g.rep[2] : 0, hi2 = (flags & 4u) ? g.rep[2] : 0;
+        for (int dx = lo0; dx <= hi0; dx++)
+            for (int dy = lo1; dy <= hi1; dy++)
+                for (int dz = lo2; dz <= hi2; dz++) {
                     T x, y, z;
                     image_pos(g, w.x, w.y, w.z, dx, dy, dz, x, y, z);
                     if ((double)x < h.clip_lo[0] || (double)x > h.clip_hi[0] || (double)y < h.clip_lo[1] || (double)y > h.clip_hi[1] ||
