@@ -300,15 +300,16 @@ rg_target_bbox_kernel(const int64_t* __restrict__ targets, int64_t Nt, int64_t N
 // grow, and once they are wider than the cutoff the scan shrinks to +-1.
 // ------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 rg_grid_kernel(DevHeader* h, double radius, long long src_capacity, long long cell_capacity, int cand_capacity,
                int force_sx, int force_sy, const unsigned long long* __restrict__ partials, int num_partials,
                const unsigned long long* __restrict__ tpartials, int num_tpartials)
 {
     {   // reduce the per-block partials of rg_wrap_kernel into the header
-        __shared__ unsigned long long red[7][8];
+        __shared__ unsigned long long red[7][32];
         unsigned long long v[7] = {~0ull, ~0ull, ~0ull, 0ull, 0ull, 0ull, 0ull};
-        for (int b = threadIdx.x; b < num_partials; b += blockDim.x) {
+#pragma unroll 4
+        for (int b = threadIdx.x; b < num_partials; b += blockDim.x) {  // independent loads, several in flight
 #pragma unroll
             for (int k = 0; k < 3; k++) {
                 v[k] = min(v[k], partials[(size_t)b * 8 + k]);
@@ -339,8 +340,9 @@ rg_grid_kernel(DevHeader* h, double radius, long long src_capacity, long long ce
     }
     __shared__ unsigned long long tbox[6];
     {   // bounding box of the target subset (if any), same block reduction
-        __shared__ unsigned long long tred[6][8];
+        __shared__ unsigned long long tred[6][32];
         unsigned long long v[6] = {~0ull, ~0ull, ~0ull, 0ull, 0ull, 0ull};
+#pragma unroll 4
         for (int b = threadIdx.x; b < num_tpartials; b += blockDim.x) {
 #pragma unroll
             for (int k = 0; k < 3; k++) {
@@ -655,6 +657,7 @@ template <typename T> struct PairParams {
     const long long* toffset; // [Nt+1]
     unsigned short* hitmask;  // [Nt, 32] per lane: bit s set if candidate 32 s + lane is a neighbour (written by COUNT)
     const uint2* smeta;       // [M] {atom id, packed shift code} per source record
+    int32_t* counts_out;      // [Nt] degrees in caller order, or nullptr
     T r2;
 };
 // The plan stores its PairParams inside the workspace (after the header) so that the fill call
@@ -683,7 +686,7 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
     DevHeader* hp = p.h;
     if (hp->status & RG_FATAL) return;
     if (MODE == MODE_FILL && skip_if_masks && hp->reserved[0] <= RG_MASK_SLOTS) return;  // rg_fillmask_kernel does it
-    int warp_max_slots = 0;
+    int warp_max_slots = 0, warp_max_degree = 0;
     const int nx = hp->nx, ny = hp->ny, nz = hp->nz, S = hp->group_cells, Sy = hp->group_cells_y, pad = hp->pad;
     const uint32_t gx = (uint32_t)hp->gx;
     const uint32_t gy = (uint32_t)((ny + Sy - 1) / Sy);
@@ -799,7 +802,12 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                     if (lane == 0) {
                         p.tcount[t] = (uint32_t)ca;
                         if (has2) p.tcount[t + 1] = (uint32_t)cb;
+                        if (!more_chunks && p.counts_out != nullptr) {  // degree in caller order (tpos.w = entry)
+                            p.counts_out[real_to_bits(tpA.w)] = ca;
+                            if (has2) p.counts_out[real_to_bits(tpB.w)] = cb;
+                        }
                     }
+                    if (!more_chunks) warp_max_degree = max(warp_max_degree, max(ca, has2 ? cb : 0));
                 } else if (MODE == MODE_COUNT) {
                     int ca = 0, cb = 0;
 #pragma unroll 2
@@ -816,7 +824,12 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                     if (lane == 0) {
                         p.tcount[t] = (uint32_t)(prodA + ca);
                         if (has2) p.tcount[t + 1] = (uint32_t)(prodB + cb);
+                        if (!more_chunks && p.counts_out != nullptr) {
+                            p.counts_out[real_to_bits(tpA.w)] = prodA + ca;
+                            if (has2) p.counts_out[real_to_bits(tpB.w)] = prodB + cb;
+                        }
                     }
+                    if (!more_chunks) warp_max_degree = max(warp_max_degree, max(prodA + ca, has2 ? prodB + cb : 0));
                 } else {
                     int4 tmA = p.tmeta[t];
                     int4 tmB = p.tmeta[has2 ? t + 1 : t];
@@ -914,6 +927,14 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
             for (int yr = 0; yr < 2; yr++)
                 for (uint32_t t = tb[yr] + lane; t < te[yr]; t += 32) p.tcount[t] = 0;
         }
+    }
+    if (MODE == MODE_COUNT) {  // largest degree: one atomic per CTA
+        __shared__ int s_max_degree;
+        if (threadIdx.x == 0) s_max_degree = 0;
+        __syncthreads();
+        if (lane == 0 && warp_max_degree > 0) atomicMax(&s_max_degree, warp_max_degree);
+        __syncthreads();
+        if (threadIdx.x == 0 && s_max_degree > 0) atomicMax(&hp->max_degree, (uint32_t)s_max_degree);
     }
     // a candidate list too long for the hit bits: the edge writer has to recompute distances
     if (MODE == MODE_COUNT && lane == 0 && warp_max_slots > RG_MASK_SLOTS) atomicMax(&hp->reserved[0], (long long)warp_max_slots);
@@ -1071,30 +1092,6 @@ rg_fillmask_kernel(const PairParams<T>* __restrict__ params_dev, long long* __re
                 }
             }
         }
-    }
-}
-
-// degree in caller order + maximum degree
-template <typename T>
-__global__ void __launch_bounds__(256)
-rg_post_count_kernel(int64_t Nt, const Vec4<T>* __restrict__ tpos, const uint32_t* __restrict__ tcount,
-                     int32_t* __restrict__ counts_out, DevHeader* __restrict__ h)
-{
-    if (h->status & RG_FATAL) return;
-    const int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    uint32_t c = 0;
-    if (k < Nt) {
-        c = tcount[k];
-        if (counts_out != nullptr) counts_out[real_to_bits(tpos[k].w)] = (int32_t)c;
-    }
-    __shared__ uint32_t wmax[8];
-    c = __reduce_max_sync(0xffffffffu, c);
-    if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = c;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        uint32_t m = 0;
-        for (int w = 0; w < 8; w++) m = max(m, wmax[w]);
-        if (m > 0) atomicMax(&h->max_degree, m);
     }
 }
 
@@ -1287,7 +1284,7 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
         for (int k = 0; k < 3; k++) { hi.bb_min[k] = ~0ull; hi.bb_max[k] = 0ull; }
         memcpy(init, &hi, sizeof(hi));
         PairParams<T> pp;
-        pp.h = h; pp.cstart = ccount; pp.tcstart = tccount; pp.spos = spos; pp.scode = scode; pp.smeta = smeta; pp.hitmask = hitmask; pp.tpos = tpos;
+        pp.h = h; pp.cstart = ccount; pp.tcstart = tccount; pp.spos = spos; pp.scode = scode; pp.smeta = smeta; pp.hitmask = hitmask; pp.counts_out = counts_out; pp.tpos = tpos;
         pp.tmeta = tmeta; pp.tcount = tcount; pp.toffset = toffset; pp.r2 = (T)radius * (T)radius;
         memcpy(init + RG_PARAMS_OFFSET, &pp, sizeof(pp));
     }
@@ -1311,7 +1308,7 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
         n_tpart = (int)((Nt + 255) / 256);
         rg_target_bbox_kernel<T><<<n_tpart, 256, 0, stream>>>(targets, Nt, N, posw, reinterpret_cast<unsigned long long*>(w + L.tpartials));
     }
-    rg_grid_kernel<T><<<1, 256, 0, stream>>>(h, radius, (long long)src_cap, (long long)cell_cap,
+    rg_grid_kernel<T><<<1, 1024, 0, stream>>>(h, radius, (long long)src_cap, (long long)cell_cap,
                                              PAIR_CAND_BYTES / (int)sizeof(Vec4<T>), force_sx, force_sy,
                                              reinterpret_cast<const unsigned long long*>(w + L.partials),
                                              (int)((N + WRAP_THREADS - 1) / WRAP_THREADS),
@@ -1320,10 +1317,10 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
     const int64_t nb = std::max(N, Nt);
     rg_bin_kernel<T, false><<<(unsigned)((nb + 255) / 256), 256, 0, stream>>>(
         N, Nt, targets, g, posw, h, ccount, cfill, tccount, tcfill, skey, scell, tkey, tcell);
-    // the scan total is the number of source images actually binned (<= the count of rg_wrap when clipping): it becomes header.M
-    DYNB_CUDA_OK((exclusive_scan<uint32_t, uint32_t>(ccount, ccount, &h->ncell_plus1, cell_cap + 1, sums32,
-                                                      reinterpret_cast<uint32_t*>(&h->M), stream)));
-    DYNB_CUDA_OK((exclusive_scan<uint32_t, uint32_t>(tccount, tccount, &h->ncell_plus1, cell_cap + 1, sums32, nullptr, stream)));
+    // cell starts of sources and targets in the same three launches; the total of the source counts is the
+    // number of source images actually binned (<= the count of rg_wrap when clipping): it becomes header.M
+    DYNB_CUDA_OK((exclusive_scan_pair<uint32_t, uint32_t>(ccount, ccount, reinterpret_cast<uint32_t*>(&h->M), tccount, tccount, nullptr,
+                                                           &h->ncell_plus1, cell_cap + 1, sums32, stream)));
     rg_bin_kernel<T, true><<<(unsigned)((nb + 255) / 256), 256, 0, stream>>>(
         N, Nt, targets, g, posw, h, ccount, cfill, tccount, tcfill, skey, scell, tkey, tcell);
     const int64_t nf = std::max(src_cap, Nt);
@@ -1334,7 +1331,6 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
     DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_COUNT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int grid = sm_count_cached() * 4 * pair_grid_waves();
     rg_pair_kernel<T, MODE_COUNT><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, nullptr, nullptr, nullptr, 0, HaloArgs{}, 0, GlueArgs{});
-    rg_post_count_kernel<T><<<(unsigned)((Nt + 255) / 256), 256, 0, stream>>>(Nt, tpos, tcount, counts_out, h);
     DYNB_CUDA_OK((exclusive_scan<uint32_t, long long>(tcount, toffset, nullptr, Nt + 1, sums64,
                                                        reinterpret_cast<long long*>(&h->E), stream)));
     DYNB_CUDA_OK(cudaGetLastError());

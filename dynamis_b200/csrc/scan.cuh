@@ -46,9 +46,8 @@ __device__ __forceinline__ int64_t scan_count(const uint32_t* n_dev, int64_t n_h
 }
 
 template <typename TIn, typename TOut>
-__global__ void __launch_bounds__(SCAN_THREADS)
-scan_tile_sums_kernel(const TIn* __restrict__ in, const uint32_t* __restrict__ n_dev, int64_t n_host,
-                      TOut* __restrict__ sums)
+__device__ __forceinline__ void scan_tile_sums_body(const TIn* __restrict__ in, const uint32_t* __restrict__ n_dev, int64_t n_host,
+                                                    TOut* __restrict__ sums)
 {
     __shared__ TOut warp_sums[SCAN_THREADS / 32];
     const int64_t n = scan_count(n_dev, n_host);
@@ -62,10 +61,26 @@ scan_tile_sums_kernel(const TIn* __restrict__ in, const uint32_t* __restrict__ n
     if (threadIdx.x == 0) sums[blockIdx.x] = tot;
 }
 
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(SCAN_THREADS)
+scan_tile_sums_kernel(const TIn* __restrict__ in, const uint32_t* __restrict__ n_dev, int64_t n_host,
+                      TOut* __restrict__ sums)
+{
+    scan_tile_sums_body<TIn, TOut>(in, n_dev, n_host, sums);
+}
+
+// two arrays of the same length in one launch: blockIdx.y picks the array, sums holds 2 x tiles entries
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(SCAN_THREADS)
+scan_tile_sums_pair_kernel(const TIn* __restrict__ in0, const TIn* __restrict__ in1, const uint32_t* __restrict__ n_dev,
+                           int64_t n_host, TOut* __restrict__ sums)
+{
+    scan_tile_sums_body<TIn, TOut>(blockIdx.y ? in1 : in0, n_dev, n_host, sums + (size_t)blockIdx.y * gridDim.x);
+}
+
 // One block scans the tile sums in place (exclusive) and publishes the grand total.
 template <typename TOut>
-__global__ void __launch_bounds__(SCAN_THREADS)
-scan_sums_kernel(TOut* __restrict__ sums, int num_tiles, TOut* __restrict__ total_out)
+__device__ __forceinline__ void scan_sums_body(TOut* __restrict__ sums, int num_tiles, TOut* __restrict__ total_out)
 {
     __shared__ TOut warp_sums[SCAN_THREADS / 32];
     TOut carry = 0;
@@ -80,10 +95,23 @@ scan_sums_kernel(TOut* __restrict__ sums, int num_tiles, TOut* __restrict__ tota
     if (threadIdx.x == 0 && total_out != nullptr) *total_out = carry;
 }
 
-template <typename TIn, typename TOut>
+template <typename TOut>
 __global__ void __launch_bounds__(SCAN_THREADS)
-scan_apply_kernel(const TIn* in, const uint32_t* __restrict__ n_dev, int64_t n_host,
-                  const TOut* __restrict__ sums, TOut* out)
+scan_sums_kernel(TOut* __restrict__ sums, int num_tiles, TOut* __restrict__ total_out)
+{
+    scan_sums_body<TOut>(sums, num_tiles, total_out);
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(SCAN_THREADS)
+scan_sums_pair_kernel(TOut* __restrict__ sums, int num_tiles, TOut* __restrict__ total0, TOut* __restrict__ total1)
+{
+    scan_sums_body<TOut>(sums + (size_t)blockIdx.x * num_tiles, num_tiles, blockIdx.x ? total1 : total0);
+}
+
+template <typename TIn, typename TOut>
+__device__ __forceinline__ void scan_apply_body(const TIn* in, const uint32_t* __restrict__ n_dev, int64_t n_host,
+                                                const TOut* __restrict__ sums, TOut* out)
 {
     __shared__ TOut warp_sums[SCAN_THREADS / 32];
     const int64_t n = scan_count(n_dev, n_host);
@@ -104,6 +132,22 @@ scan_apply_kernel(const TIn* in, const uint32_t* __restrict__ n_dev, int64_t n_h
     }
 }
 
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(SCAN_THREADS)
+scan_apply_kernel(const TIn* in, const uint32_t* __restrict__ n_dev, int64_t n_host,
+                  const TOut* __restrict__ sums, TOut* out)
+{
+    scan_apply_body<TIn, TOut>(in, n_dev, n_host, sums, out);
+}
+
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(SCAN_THREADS)
+scan_apply_pair_kernel(const TIn* in0, TOut* out0, const TIn* in1, TOut* out1, const uint32_t* __restrict__ n_dev, int64_t n_host,
+                       const TOut* __restrict__ sums)
+{
+    scan_apply_body<TIn, TOut>(blockIdx.y ? in1 : in0, n_dev, n_host, sums + (size_t)blockIdx.y * gridDim.x, blockIdx.y ? out1 : out0);
+}
+
 static inline int scan_num_tiles(int64_t n_host) { return (int)((n_host + SCAN_TILE - 1) / SCAN_TILE); }
 
 // `sums` must hold scan_num_tiles(n_host) elements of TOut.  `total_out` (device, may be null)
@@ -120,6 +164,20 @@ static inline cudaError_t exclusive_scan(const TIn* in, TOut* out, const uint32_
     scan_tile_sums_kernel<TIn, TOut><<<tiles, SCAN_THREADS, 0, stream>>>(in, n_dev, n_host, sums);
     scan_sums_kernel<TOut><<<1, SCAN_THREADS, 0, stream>>>(sums, tiles, total_out);
     scan_apply_kernel<TIn, TOut><<<tiles, SCAN_THREADS, 0, stream>>>(in, n_dev, n_host, sums, out);
+    return cudaGetLastError();
+}
+
+// Two arrays of the same (possibly device-side) length in the same three launches.  `sums` must hold
+// 2 x scan_num_tiles(n_host) elements.
+template <typename TIn, typename TOut>
+static inline cudaError_t exclusive_scan_pair(const TIn* in0, TOut* out0, TOut* total0, const TIn* in1, TOut* out1, TOut* total1,
+                                              const uint32_t* n_dev, int64_t n_host, TOut* sums, cudaStream_t stream)
+{
+    if (n_host <= 0) return cudaSuccess;
+    const int tiles = scan_num_tiles(n_host);
+    scan_tile_sums_pair_kernel<TIn, TOut><<<dim3(tiles, 2), SCAN_THREADS, 0, stream>>>(in0, in1, n_dev, n_host, sums);
+    scan_sums_pair_kernel<TOut><<<2, SCAN_THREADS, 0, stream>>>(sums, tiles, total0, total1);
+    scan_apply_pair_kernel<TIn, TOut><<<dim3(tiles, 2), SCAN_THREADS, 0, stream>>>(in0, out0, in1, out1, n_dev, n_host, sums);
     return cudaGetLastError();
 }
 

@@ -311,9 +311,9 @@ def owned_graph(positions: torch.Tensor, cell: torch.Tensor, pbc: torch.Tensor, 
 
 def launches_per_graph() -> int:
     """Kernels one radius_graph_pbc call launches: zero-degrees, wrap, grid, cell histogram,
-    2 x 3 scan kernels (source and target cells), scatter, finalize, count pass, degree post-pass,
+    3 scan kernels (source and target cell starts together), scatter, finalize, count pass (degrees included),
     3 scan kernels (edge offsets), two edge-writing launches (the one driven by the hit bits of the
     count pass and the one that recomputes distances; the device decides which of them does the work, the
     other returns at once; with distances requested only the second is launched).  One more, the target
     bounding box, with a target subset."""
-    return 19
+    return 15
