@@ -596,6 +596,16 @@ __device__ __forceinline__ void runs_compact(int* delta, int run_a, int run_off,
     const uint32_t nem = __ballot_sync(0xffffffffu, run_len > 0);
     if (run_len > 0) delta[__popc(nem & lt)] = run_a - run_off;
 }
+// Asynchronous global -> shared copies (LDGSTS): the records of a whole chunk are requested back to back
+// without passing through registers; cp_async_wait_all() before the warp reads them.
+template <int BYTES>
+__device__ __forceinline__ void cp_async(void* smem_dst, const void* gsrc)
+{
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(d), "l"(gsrc), "n"(BYTES) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 // returns the number of non-empty runs that start before cbeg; flags covers [cbeg, cbeg + 32 * RUN_FLAG_WORDS)
 __device__ __forceinline__ int runs_flags(uint32_t* flags, int run_off, int run_len, int lane, int cbeg)
 {
@@ -621,6 +631,10 @@ struct HaloArgs {
     int words;
 };
 
+#ifndef DYNB_COUNT_UNROLL
+#define DYNB_COUNT_UNROLL 2
+#endif
+constexpr int COUNT_UNROLL = DYNB_COUNT_UNROLL;  // unroll factor of the count pass's test loop (tuning knob at build time)
 constexpr int RG_MASK_SLOTS = 16;  // hit bits kept per lane and target (candidate lists up to 512 records)
 
 // Optional extras of the edge writers for the model-side glue: the shifts written with the caller's sign
@@ -748,8 +762,13 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                 rank_base += __popc(word);
                 if (j < clen) {
                     const int gidx = delta[r] + cbeg + j;
-                    cand[j] = p.spos[gidx];  // w = atom id
-                    if (MODE == MODE_FILL) codes[j] = p.scode[gidx];
+                    if (sizeof(Vec4<T>) == 16) {
+                        cp_async<16>(&cand[j], &p.spos[gidx]);  // w = atom id
+                    } else {
+                        cp_async<16>(&cand[j], &p.spos[gidx]);
+                        cp_async<16>(reinterpret_cast<char*>(&cand[j]) + 16, reinterpret_cast<const char*>(&p.spos[gidx]) + 16);
+                    }
+                    if (MODE == MODE_FILL) cp_async<4>(&codes[j], &p.scode[gidx]);
                 }
             }
             if (clen + lane < clen32) {
@@ -758,6 +777,7 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                 c.w = (T)0;
                 cand[clen + lane] = c;
             }
+            cp_async_wait_all();
             __syncwarp();
 
 #pragma unroll
@@ -785,7 +805,7 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                         bitsB = mrowB[lane];
                     }
                     uint32_t bit = 1u << (cbeg >> 5);
-#pragma unroll 2
+#pragma unroll COUNT_UNROLL
                     for (int k = 0; k < clen32; k += 32) {
                         const Vec4<T> c = cand[k + lane];
                         const T sx = c.x, sy = c.y, sz = c.z;
@@ -1034,7 +1054,8 @@ rg_fillmask_kernel(const PairParams<T>* __restrict__ params_dev, long long* __re
         __syncwarp();
         runs_compact(delta, run_a, run_off, run_len, lt);
         int rank_base = runs_flags(flags, run_off, run_len, lane, 0);
-        // four slots at a time: the four gathers are in flight together before the first is stored
+        // four slots at a time: the four gathers are in flight together before the first is stored (measured
+        // against asynchronous 8-byte copies into shared memory: equal on sparse cells, faster on dense ones)
         for (int sw0 = 0; sw0 < nslots; sw0 += 4) {
             uint2 mv[4];
 #pragma unroll
