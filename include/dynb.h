@@ -109,8 +109,11 @@ int dynb_rg_halo_mark(const void* workspace_dev, int dtype, const int64_t* owner
  * Replaces sfc_partition_cuda (dynamis_state/src/csrc/partition/sfc.cpp:9-33,
  * sfc_kernels.cu:178-251): labels_dev[i] in [0, W) for every atom.  curve_type 0 = Morton
  * (21 bits per axis), 1 = the reference's 7-bit "Hilbert" transform.  weights_dev: int64 per-atom
- * cost or NULL (equal counts).  perm_dev (optional): atom indices in curve order.
- * Atoms with equal keys are ordered by ascending index (the reference leaves ties unspecified). */
+ * cost (non-negative) or NULL (equal counts).  perm_dev (optional): atom indices in curve order.
+ * Atoms with equal keys are ordered by ascending index (the reference leaves ties unspecified).
+ * With perm_dev == NULL, W <= 1025 and the full workspace, the labels come from a digit-by-digit
+ * selection of the W - 1 split points on (key, index) instead of a sort (same labels, about a third of
+ * the time); a workspace of the sorted path's size alone selects the sorted path. */
 int dynb_sfc_workspace_bytes(int64_t n_atoms, int64_t* bytes);
 int dynb_sfc_partition(const float* pos_dev, int64_t n_atoms, const int64_t* weights_dev, int64_t W, int curve_type,
                        int64_t* labels_dev, int64_t* perm_dev, void* workspace_dev, int64_t workspace_bytes,
