@@ -47,7 +47,7 @@ SIGNATURES = {
     "dynb_rg_workspace_bytes": (_i32, [_i64, _i64, _i64, _i64, _i32, ctypes.POINTER(_i64)]),
     "dynb_rg_plan": (_i32, [_p, _i32, _i64, _p, _p, _f64, _p, _i64, _p, _i64, _i64, _i64, _p, _p, _p]),
     "dynb_rg_fill": (_i32, [_p, _i32, _p, _p, _p, _i64, _p]),
-    "dynb_rg_fill_glue": (_i32, [_p, _i32, _p, _p, _p, _p, _i32, _i64, _p]),
+    "dynb_rg_fill_glue": (_i32, [_p, _i32, _p, _p, _p, _p, _i32, _p, _i64, _p]),
     "dynb_rg_halo_mark": (_i32, [_p, _i32, _p, _i64, _i64, _p, _p, _p]),
     "dynb_sfc_workspace_bytes": (_i32, [_i64, ctypes.POINTER(_i64)]),
     "dynb_sfc_partition": (_i32, [_p, _i64, _p, _i64, _i32, _p, _p, _p, _i64, _p]),

@@ -641,9 +641,10 @@ constexpr int RG_MASK_SLOTS = 16;  // hit bits kept per lane and target (candida
 // and the Cartesian shift of every edge, unit_shift @ cell, rounded like a K = 3 float GEMM
 // (products and sums of torch.matmul(unit_shifts, cell): fma(u2, c2, fma(u1, c1, u0 * c0))).
 struct GlueArgs {
-    float* cart;  // [E,3] or nullptr
-    int negate;   // 1: write -shift
-    float c[9];   // cell, row-major
+    float* cart;              // [E,3] or nullptr
+    const long long* id_map;  // [n_atoms] ids to write instead of the atom indices (local -> global), or nullptr
+    int negate;               // 1: write -shift
+    float c[9];               // cell, row-major
 };
 __device__ __forceinline__ void glue_write(const GlueArgs& g, float* __restrict__ shifts, long long e, int ix, int iy, int iz)
 {
@@ -910,8 +911,9 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                                         const Vec4<T> ch = cand[jh];
                                         const uint32_t code = codes[jh];
                                         const long long e = bX + i;
-                                        ei[e] = (long long)real_to_bits(ch.w);
-                                        ei[E + e] = (long long)tm.x;
+                                        const long long sa = (long long)real_to_bits(ch.w);
+                                        ei[e] = glue.id_map ? glue.id_map[sa] : sa;
+                                        ei[E + e] = glue.id_map ? glue.id_map[tm.x] : (long long)tm.x;
                                         glue_write(glue, shifts, e, (int)(code & 1023u) - 512 + tm.y, (int)((code >> 10) & 1023u) - 512 + tm.z,
                                                    (int)((code >> 20) & 1023u) - 512 + tm.w);
                                         if (d2out != nullptr) {
@@ -1098,12 +1100,13 @@ rg_fillmask_kernel(const PairParams<T>* __restrict__ params_dev, long long* __re
             }
             __syncwarp();
             const int sx = tm.y - 512, sy = tm.z - 512, sz = tm.w - 512;
+            const long long dst_id = (GLUE && glue.id_map) ? glue.id_map[tm.x] : (long long)tm.x;
             for (int i = lane; i < cnt; i += 32) {
                 const uint2 m = meta[list[i]];
                 const uint32_t code = m.y;
                 const long long e = base + i;
-                ei[e] = (long long)m.x;
-                ei[E + e] = (long long)tm.x;
+                ei[e] = (GLUE && glue.id_map) ? glue.id_map[m.x] : (long long)m.x;
+                ei[E + e] = dst_id;
                 if (GLUE) {
                     glue_write(glue, shifts, e, (int)(code & 1023u) + sx, (int)((code >> 10) & 1023u) + sy, (int)((code >> 20) & 1023u) + sz);
                 } else {
@@ -1469,7 +1472,8 @@ extern "C" int dynb_rg_fill(const void* workspace_dev, int dtype, int64_t* edge_
 }
 
 extern "C" int dynb_rg_fill_glue(const void* workspace_dev, int dtype, int64_t* edge_index_dev, float* unit_shifts_dev,
-                                 float* cart_shifts_dev, const float* cell_host, int negate_shifts, int64_t E, void* stream)
+                                 float* cart_shifts_dev, const float* cell_host, int negate_shifts, const int64_t* id_map_dev,
+                                 int64_t E, void* stream)
 {
     if (workspace_dev == nullptr) return fail_arg("null workspace");
     if (E < 0) return fail_arg("E must be non-negative");
@@ -1479,6 +1483,7 @@ extern "C" int dynb_rg_fill_glue(const void* workspace_dev, int dtype, int64_t* 
     if (edge_index_dev == nullptr || unit_shifts_dev == nullptr) return fail_arg("null output pointer");
     GlueArgs g{};
     g.cart = cart_shifts_dev;
+    g.id_map = reinterpret_cast<const long long*>(id_map_dev);
     g.negate = negate_shifts;
     for (int k = 0; k < 9; k++) g.c[k] = cell_host != nullptr ? cell_host[k] : 0.0f;
     cudaStream_t s = static_cast<cudaStream_t>(stream);

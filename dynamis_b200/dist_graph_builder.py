@@ -21,7 +21,7 @@ from typing import Optional
 
 import torch
 
-from .graph import radius_graph_pbc_counts_ex, radius_graph_pbc_ex
+from .graph import plan_radius_graph, radius_graph_pbc_counts_ex, radius_graph_pbc_ex
 from .halo import extract_halo_info, filter_edges_to_radius
 from .partition import SFCCurveType, SFCPartitioner, select_eq
 from .state import DistEnvironment, MolecularInfo, PartitionMessagePassingInfo
@@ -169,12 +169,14 @@ class DistGraphBuilder:
         owned_and_halo = torch.cat([self._my_outer_atoms, self._halo_recv_global_ids])
         local_pos = pos_w.index_select(0, owned_and_halo).contiguous()
         targets = torch.arange(self._my_outer_atoms.numel(), dtype=torch.int64, device=dev)
-        e_loc, shifts, _, _ = radius_graph_pbc_ex(local_pos, cell, pbc, self.cutoff, self.max_num_neighbors,
-                                                  self.enforce_max_strictly, targets)
-        if e_loc.numel() == 0:
+        if targets.numel() == 0 or local_pos.size(0) == 0:
             edges = torch.empty(2, 0, dtype=torch.int64, device=dev)
+            shifts = torch.empty(0, 3, dtype=torch.float32, device=dev)
         else:
-            edges = owned_and_halo[e_loc]  # local -> global ids, both rows at once
+            # same graph as radius_graph_pbc_ex(local_pos, ..., targets); the edge writer stores the global ids
+            # directly (the reference maps both rows through owned_and_halo in a second pass over the edges)
+            plan = plan_radius_graph(local_pos, cell, pbc, float(self.cutoff), targets)
+            edges, shifts, _ = plan.fill_glue(None, negate_shifts=False, cartesian=False, id_map=owned_and_halo.contiguous())
         self._steps_since_refresh += 1
         return DistBuildGraphResult(edges, shifts, self._pid_outer, self._my_outer_atoms, self._halo_info,
                                     self._interior_mask, self._full_degrees, self._halo_recv_global_ids, BuildMode.STEADY)

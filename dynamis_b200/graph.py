@@ -107,9 +107,11 @@ class RadiusGraphPlan:
                    "rg_fill")
 
 
-    def fill_glue(self, cell: torch.Tensor, negate_shifts: bool = True, cartesian: bool = True):
-        """Edge list with the shifts in the caller's sign and, optionally, the Cartesian shifts
-        ``unit_shifts @ cell`` (float32), written by the edge writer itself."""
+    def fill_glue(self, cell: Optional[torch.Tensor], negate_shifts: bool = True, cartesian: bool = True,
+                  id_map: Optional[torch.Tensor] = None):
+        """Edge list with the shifts in the caller's sign, optionally the Cartesian shifts
+        ``unit_shifts @ cell`` (float32) and ids mapped through ``id_map`` (local -> global), all written by
+        the edge writer itself."""
         dev = self.device
         E = self.E
         with torch.cuda.device(dev):
@@ -117,11 +119,18 @@ class RadiusGraphPlan:
             unit = torch.empty((E, 3), dtype=torch.float32, device=dev)
             cart = torch.empty((E, 3), dtype=torch.float32, device=dev) if cartesian else None
             if E:
-                cell_h = np.ascontiguousarray(cell.detach().to("cpu").reshape(3, 3).numpy().astype(np.float32))
+                cell_h = None
+                if cartesian:
+                    cell_h = np.ascontiguousarray(cell.detach().to("cpu").reshape(3, 3).numpy().astype(np.float32))
+                if id_map is not None:
+                    if id_map.dtype != torch.int64 or not id_map.is_contiguous() or id_map.device != dev:
+                        raise RuntimeError("id_map must be a contiguous int64 tensor on the graph's device")
                 stream = torch.cuda.current_stream(dev)
                 _lib.check(_lib.lib().dynb_rg_fill_glue(self.ws.data_ptr(), self.dtype_code, edge_index.data_ptr(), unit.data_ptr(),
-                                                        cart.data_ptr() if cart is not None else None, cell_h.ctypes.data,
-                                                        1 if negate_shifts else 0, E, stream.cuda_stream), "rg_fill_glue")
+                                                        cart.data_ptr() if cart is not None else None,
+                                                        cell_h.ctypes.data if cell_h is not None else None,
+                                                        1 if negate_shifts else 0, id_map.data_ptr() if id_map is not None else None,
+                                                        E, stream.cuda_stream), "rg_fill_glue")
         return edge_index, unit, cart
 
 

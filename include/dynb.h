@@ -62,7 +62,8 @@ typedef struct dynb_rg_header {
     int32_t grid[3];    /* cell grid dimensions chosen on the device */
     int32_t group_cells;/* cells per warp work item along x */
     int64_t num_groups;
-    int64_t reserved[2];
+    int64_t reserved[2]; /* [0]: 0, or the longest candidate list in 32-record slots when it exceeded the 16 slots the
+                          * count pass keeps hit bits for (dynb_rg_fill then recomputes the distances); [1]: unused */
 } dynb_rg_header;
 
 /* Suggested capacities for a system: src_capacity bounds the number of periodic images
@@ -92,10 +93,13 @@ int dynb_rg_fill(const void* workspace_dev, int dtype, int64_t* edge_index_dev /
  * float32 — three more passes over the edge list.  Here the owned-destination filter is the plan's
  * target subset 0..num_local-1, negate_shifts = 1 writes the offsets negated, and cart_shifts_dev
  * (optional, may be NULL) receives unit_shifts @ cell_host (9 floats, row-major) with the rounding of
- * a K = 3 float32 GEMM. */
+ * a K = 3 float32 GEMM.  id_map_dev (optional, may be NULL; n_atoms entries): ids written into
+ * edge_index instead of the atom indices — the local -> global mapping DistGraphBuilder applies to both
+ * rows after a steady-state build (dynamis_state/src/dynamis_state/dist_graph_builder.py:441-470). */
 int dynb_rg_fill_glue(const void* workspace_dev, int dtype, int64_t* edge_index_dev /* [2,E] */,
                       float* unit_shifts_dev /* [E,3] */, float* cart_shifts_dev /* [E,3] or NULL */,
-                      const float* cell_host /* [9] */, int negate_shifts, int64_t E, void* stream);
+                      const float* cell_host /* [9] */, int negate_shifts, const int64_t* id_map_dev,
+                      int64_t E, void* stream);
 
 /* Halo marking over a plan (all atoms as targets, radius = cutoff + ghost buffer): for every edge
  * src -> dst whose endpoints have different owners, sets bit owner[dst] of

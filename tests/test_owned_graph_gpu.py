@@ -82,6 +82,12 @@ def test_owned_graph_signs_and_optional_outputs(cuda):
     e2, s2, _, _ = D.radius_graph_pbc_ex(tp, tc, tb, r, 0, False, torch.arange(3000, device=cuda))
     assert torch.equal(e2, ei_p) and torch.equal(s2, unit_p)
     assert bool((unit_n != 0).any())               # the box is periodic: some edges cross it
+    # ids written through a map (local -> global, as DistGraphBuilder's steady build needs them)
+    from dynamis_b200.graph import plan_radius_graph
+    gid = torch.randperm(5_000, device=cuda) + 1_000_000
+    plan = plan_radius_graph(tp, tc, tb, r, torch.arange(3000, device=cuda))
+    e_map, s_map, _ = plan.fill_glue(None, negate_shifts=False, cartesian=False, id_map=gid)
+    assert torch.equal(e_map, gid[ei_p]) and torch.equal(s_map, unit_p)
 
 
 def test_owned_graph_degenerate(cuda):
@@ -95,5 +101,5 @@ def test_owned_graph_degenerate(cuda):
     from dynamis_b200 import _lib
 
     lib = _lib.lib()
-    assert lib.dynb_rg_fill_glue(None, 0, None, None, None, None, 1, 5, None) != 0
+    assert lib.dynb_rg_fill_glue(None, 0, None, None, None, None, 1, None, 5, None) != 0
     assert b"workspace" in lib.dynb_last_error()

@@ -11,6 +11,7 @@ import numpy as np
 import pytest
 import torch
 
+import dynamis_b200 as D
 from _util import assert_same_edges, canon_o, canon_t, digest_t
 from dynamis_b200 import synthetic
 from oracle import cpu_oracle as O
@@ -49,6 +50,23 @@ def _cubic(n, box, seed, dtype=np.float32):
 def test_cubic(cuda, n, box, r):
     pos, cell, pbc = _cubic(n, box, 42 + n)
     _check_vs_oracle(pos, cell, pbc, r, cuda, what=f"cubic{n}")
+
+
+def test_dense_cells_long_candidate_lists(cuda):
+    """Candidate lists far beyond the 512 records the count pass keeps hit bits for: the edge list is then
+    written by the distance-recomputing writer, walking each list in several chunks; with distances
+    requested that writer is used for every input.  Both must agree with the oracle and with each other."""
+    pos, cell, pbc = _cubic(3000, 10.0, 91)          # 3 atoms / A^3, ~340 neighbours each
+    ei, cs, g = _check_vs_oracle(pos, cell, pbc, 3.0, cuda, what="dense")
+    assert g["E"] > 900_000
+    out = D.radius_graph_pbc_with_dist(torch.as_tensor(pos, device=cuda), torch.as_tensor(cell), torch.tensor(pbc), 3.0)
+    assert_same_edges(canon_t(out[0], out[1]), canon_t(ei, cs), "dense, with distances")
+    # a sparse case through both writers: same edge set (the order inside a target's run may differ)
+    pos, cell, pbc = _cubic(5000, 40.0, 92)
+    a = _run_ours(pos, cell, pbc, 5.0, cuda)
+    b = D.radius_graph_pbc_with_dist(torch.as_tensor(pos, device=cuda), torch.as_tensor(cell), torch.tensor(pbc), 5.0)
+    assert_same_edges(canon_t(a[0], a[1]), canon_t(b[0], b[1]), "sparse, both writers")
+    assert torch.equal(a[0][1], b[0][1])              # targets' runs are the same ranges
 
 
 def test_cutoff_larger_than_half_box(cuda):
