@@ -180,10 +180,15 @@ def run(args, rank: int, world: int, dev: torch.device):
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"random liquid {n_total} atoms ({B.ATOMS_PER_GPU}/GPU), density 0.1, fp32, cutoff 5.0 A, "
                                    f"Morton partition into {world} subdomains, halo {r + HALO_BUFFER} A: per step 1 position push (F=3), "
-                                   f"owned-atom radius graph over [owned|halo], 2 embedding pushes (F={F_EMB}), 3 reverse pushes",
+                                   f"owned-atom radius graph over [owned|halo], 2 embedding pushes (F={F_EMB}), 3 reverse pushes "
+                                   "(the N = 1 step is radius graph + Morton sort and has no exchange: compare graph_edges_per_s across N)",
                        "edges_per_step": E_total, "exchange": kind, "atoms_local_max": int(mx[1]), "halo_atoms_max": int(mx[2]),
                        "l2": "256 MiB buffer written between timed steps", "setup_s": setup_s},
             "halo_exchange_ms_per_step": xms, "graph_ms_per_step": gms,
+            # the two halves of the metric ("radius-graph edges/s and per-step halo-exchange latency") separately:
+            # `value` divides by the whole step, which at N > 1 also holds six halo exchanges that the N = 1 step
+            # (radius graph + Morton sort, no peers) does not have
+            "graph_edges_per_s": E_total / (gms * 1e-3),
             "nvlink": {"bytes_sent_per_rank_per_step": bytes_rank, "achieved_gbs": bytes_rank / (xms * 1e-3) / 1e9,
                        "peak_gbs": NVLINK_PEER_GBS, "peak_kind": "measured peer copy per direction",
                        "frac": bytes_rank / (xms * 1e-3) / 1e9 / NVLINK_PEER_GBS},
