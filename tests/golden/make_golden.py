@@ -4,6 +4,7 @@ Run on a machine with a GPU after `python oracle/build_ref.py` built oracle/_ref
 reference tree:
 
     python tests/golden/make_golden.py [out.npz]
+    python tests/golden/make_golden.py --kdtree [out.npz]     # reference_vectors_kdtree.npz
 
 Every vector is an output of the unmodified reference implementation (radius_graph_pbc_cuda_impl_ex,
 sfc_partition_cuda_impl, extract_halo_info_cuda_impl, filter_edges_to_radius_cuda_impl) on seeded
@@ -63,6 +64,39 @@ def halo_case():
     return pos, cell, pid, W
 
 
+def kdtree_case():
+    """3000 positions whose coordinates are distinct per axis (the reference's sort leaves ties open) and
+    weights whose sums stay far below 2**24 (its float32 cumulative sum is exact there)."""
+    rng = np.random.default_rng(2024)
+    n = 3000
+    pos = np.empty((n, 3), dtype=np.float32)
+    for d, scale in enumerate((30.0, 12.0, 20.0)):
+        ramp = (np.arange(n, dtype=np.float64) + rng.random(n) * 0.5) * (scale / n)
+        pos[:, d] = rng.permutation(ramp).astype(np.float32)
+        assert np.unique(pos[:, d]).size == n
+    w = rng.integers(1, 60, n).astype(np.int64)
+    return pos, w
+
+
+def main_kdtree(path):
+    """tests/golden/reference_vectors_kdtree.npz: labels of the reference's kdtree_bisect_cuda_impl."""
+    import torch
+
+    from oracle import build_ref
+
+    assert build_ref.load(), "oracle/_ref/libdynamis_ref.so is missing: run python oracle/build_ref.py"
+    ref = torch.ops.dynamis_ref
+    dev = torch.device("cuda:0")
+    pos, w = kdtree_case()
+    tp, tw = torch.as_tensor(pos, device=dev), torch.as_tensor(w, device=dev)
+    out = {}
+    for W in (2, 3, 5, 8, 13):
+        out[f"kd_W{W}"] = ref.kdtree_partition(tp, None, W).cpu().numpy().astype(np.int16)
+        out[f"kd_weighted_W{W}"] = ref.kdtree_partition(tp, tw, W).cpu().numpy().astype(np.int16)
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes,", len(out), "arrays")
+
+
 def main():
     import torch
 
@@ -106,4 +140,8 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    if "--kdtree" in sys.argv:
+        rest = [a for a in sys.argv[1:] if a != "--kdtree"]
+        main_kdtree(rest[0] if rest else os.path.join(ROOT, "tests", "golden", "reference_vectors_kdtree.npz"))
+    else:
+        main()

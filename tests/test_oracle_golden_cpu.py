@@ -78,6 +78,17 @@ def test_sfc_labels_match_reference_vectors(W):
     np.testing.assert_array_equal(np.bincount(O.sfc_partition(pos, None, W, 1), minlength=W), G[f"sfc_hilbert_counts_W{W}"])
 
 
+@pytest.mark.parametrize("W", [2, 3, 5, 8, 13])
+def test_kdtree_labels_match_reference_vectors(W):
+    """The numpy restatement of the KD-tree bisection against labels the reference's own CUDA kernels
+    produced on a B200 (tests/golden/make_golden.py --kdtree)."""
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_vectors_kdtree.npz")
+    kd = np.load(path)
+    pos, w = mg.kdtree_case()
+    np.testing.assert_array_equal(O.kdtree_partition(pos, None, W), kd[f"kd_W{W}"].astype(np.int64))
+    np.testing.assert_array_equal(O.kdtree_partition(pos, w, W), kd[f"kd_weighted_W{W}"].astype(np.int64))
+
+
 def test_sfc_invariants():
     rng = np.random.default_rng(0)
     pos = (rng.random((1001, 3)) * 30).astype(np.float32)
