@@ -15,11 +15,16 @@
 // reference converts them to float32 and uses a float cumulative sum (identical while every partial
 // sum is below 2^24; beyond that the reference's own result depends on the summation order); bounding
 // boxes are reduced per block in shared memory instead of one atomic per atom and axis.
+// With equal counts the sort is not needed at all: the cut of a segment is the atom of rank mid in
+// (coordinate, index) order, found for all segments of a level at once by the digit-by-digit selection
+// of select.cuh on (segment, coordinate, index); an atom goes right when it is not in front of its
+// segment's cut.  Weighted cuts keep the sorted path (they need ranks for the clamp).
 
 #include <vector>
 
 #include "common.cuh"
 #include "scan.cuh"
+#include "select.cuh"
 
 namespace dynb {
 
@@ -110,7 +115,8 @@ kd_gather_weights_kernel(const int64_t* __restrict__ w, const uint32_t* __restri
 // exclusive prefix of the sorted weights, excl[n] = total.
 __global__ void __launch_bounds__(256)
 kd_split_kernel(int S, const KdSeg* __restrict__ seg, const long long* __restrict__ seg_size, const long long* __restrict__ seg_start,
-                const long long* __restrict__ excl, long long* __restrict__ mid, long long* __restrict__ next_size)
+                const long long* __restrict__ excl, long long* __restrict__ mid, long long* __restrict__ next_size,
+                long long* __restrict__ thresholds /* or nullptr: 1 + atoms in front of the cut, in sorted order */)
 {
     const int s = blockIdx.x * blockDim.x + threadIdx.x;
     if (s >= S) return;
@@ -133,6 +139,7 @@ kd_split_kernel(int S, const KdSeg* __restrict__ seg, const long long* __restric
         m = min(max(lo, 1ll), sz - 1);
     }
     mid[s] = m;
+    if (thresholds != nullptr) thresholds[s] = seg_start[s] + m + 1;
     if (g.child_left == g.child_right) {
         next_size[g.child_left] = sz;
     } else {
@@ -152,6 +159,22 @@ kd_assign_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restrict__
     new_seg_id[vals[q]] = (q - seg_start[s] < mid[s]) ? g.child_left : g.child_right;
 }
 
+// equal counts without a sort: an atom goes right when its (coordinate, index) is not in front of its segment's cut
+__global__ void __launch_bounds__(256)
+kd_assign_select_kernel(const uint64_t* __restrict__ keys, int64_t n, int idx_bits, const SelSplit* __restrict__ cut,
+                        const KdSeg* __restrict__ seg, int32_t* __restrict__ new_seg_id)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint64_t key = keys[i];
+    const int s = (int)(key >> 32);
+    const SelSplit c = cut[s];
+    const u128 C = ((u128)key << idx_bits) | (u128)(uint64_t)i;
+    const bool right = !c.dead && C >= sel_prefix(c);
+    const KdSeg g = seg[s];
+    new_seg_id[i] = right ? g.child_right : g.child_left;
+}
+
 __global__ void __launch_bounds__(256)
 kd_label_kernel(const int32_t* __restrict__ seg_id, const int64_t* __restrict__ base_label, int64_t* __restrict__ labels, int64_t n)
 {
@@ -159,7 +182,7 @@ kd_label_kernel(const int32_t* __restrict__ seg_id, const int64_t* __restrict__ 
     if (i < n) labels[i] = base_label[seg_id[i]];
 }
 
-struct KdLayout { int64_t keys, vals, seg_a, seg_b, sorted_w, excl, sums, tree, size_a, size_b, start, mid, box, base_label, rs, total; };
+struct KdLayout { int64_t keys, vals, seg_a, seg_b, sorted_w, excl, sums, tree, size_a, size_b, start, mid, thr, box, base_label, rs, sel_state, sel_hist, total; };
 static KdLayout kd_layout(int64_t n, int64_t W)
 {
     KdLayout L;
@@ -179,9 +202,12 @@ static KdLayout kd_layout(int64_t n, int64_t W)
     L.size_b = take((W + 1) * 8);
     L.start = take((W + 2) * 8);
     L.mid = take((W + 1) * 8);
+    L.thr = take((W + 1) * 8);
     L.box = take(W * 6 * 4);
     L.base_label = take((W + 1) * 8);
     L.rs = take(rs_bytes);
+    L.sel_state = take(2 * SEL_MAX_SPLITS * (int64_t)sizeof(SelSplit));
+    L.sel_hist = take(2 * SEL_HIST_BYTES);
     L.total = o;
     return L;
 }
@@ -227,6 +253,8 @@ extern "C" int dynb_kdtree_partition(const float* pos_dev, int64_t n_atoms, cons
     long long* size_next = reinterpret_cast<long long*>(ws + L.size_b);
     long long* start = reinterpret_cast<long long*>(ws + L.start);
     long long* mid = reinterpret_cast<long long*>(ws + L.mid);
+    long long* thr = reinterpret_cast<long long*>(ws + L.thr);
+    const bool by_selection = (weights_dev == nullptr) && W <= SEL_MAX_SPLITS && getenv("DYNB_KD_SORT") == nullptr;  // env: testing knob
     uint32_t* box = reinterpret_cast<uint32_t*>(ws + L.box);
     int64_t* base_label = reinterpret_cast<int64_t*>(ws + L.base_label);
     int64_t rs_bytes = 0;
@@ -265,17 +293,26 @@ extern "C" int dynb_kdtree_partition(const float* pos_dev, int64_t n_atoms, cons
         kd_keys_kernel<<<nbk, 256, 0, s>>>(pos_dev, seg_cur, n, box, keys, vals);
         int seg_bits = 0;
         while ((1 << seg_bits) < S) seg_bits++;
-        const int end_bit = std::min(64, ((32 + seg_bits + 7) / 8) * 8);
-        int rc = dynb_radix_sort_pairs(keys, vals, n, 0, end_bit, ws + L.rs, rs_bytes, s);
-        if (rc) return rc;
-        const long long* excl_arg = nullptr;
-        if (weights_dev != nullptr) {
-            kd_gather_weights_kernel<<<nbk, 256, 0, s>>>(weights_dev, vals, sorted_w, n);
-            DYNB_CUDA_OK((exclusive_scan<long long, long long>(reinterpret_cast<long long*>(sorted_w), excl, nullptr, n, sums, excl + n, s)));
-            excl_arg = excl;
+        if (by_selection) {
+            kd_split_kernel<<<(S + 255) / 256, 256, 0, s>>>(S, tree, size_cur, start, nullptr, mid, size_next, thr);
+            int idx_bits = 0;
+            const SelSplit* cut = nullptr;
+            int rc = sel_select_splits(keys, 32 + seg_bits, nullptr, n, S, W, thr, ws + L.sel_state, ws + L.sel_hist, &idx_bits, &cut, true, s);
+            if (rc) return rc;
+            kd_assign_select_kernel<<<nbk, 256, 0, s>>>(keys, n, idx_bits, cut, tree, seg_next);
+        } else {
+            const int end_bit = std::min(64, ((32 + seg_bits + 7) / 8) * 8);
+            int rc = dynb_radix_sort_pairs(keys, vals, n, 0, end_bit, ws + L.rs, rs_bytes, s);
+            if (rc) return rc;
+            const long long* excl_arg = nullptr;
+            if (weights_dev != nullptr) {
+                kd_gather_weights_kernel<<<nbk, 256, 0, s>>>(weights_dev, vals, sorted_w, n);
+                DYNB_CUDA_OK((exclusive_scan<long long, long long>(reinterpret_cast<long long*>(sorted_w), excl, nullptr, n, sums, excl + n, s)));
+                excl_arg = excl;
+            }
+            kd_split_kernel<<<(S + 255) / 256, 256, 0, s>>>(S, tree, size_cur, start, excl_arg, mid, size_next, nullptr);
+            kd_assign_kernel<<<nbk, 256, 0, s>>>(keys, vals, n, tree, start, mid, seg_next);
         }
-        kd_split_kernel<<<(S + 255) / 256, 256, 0, s>>>(S, tree, size_cur, start, excl_arg, mid, size_next);
-        kd_assign_kernel<<<nbk, 256, 0, s>>>(keys, vals, n, tree, start, mid, seg_next);
         std::swap(seg_cur, seg_next);
         std::swap(size_cur, size_next);
         cur_parts.swap(next_parts);

@@ -11,6 +11,7 @@
 
 #include "common.cuh"
 #include "scan.cuh"
+#include "select.cuh"
 
 namespace dynb {
 
@@ -311,18 +312,6 @@ __global__ void __launch_bounds__(256) u32_to_i64_kernel(const uint32_t* a, int6
 // is crossed.  Six levels of 16 bits cover Morton keys of a million atoms: 12 small launches instead
 // of the 40 of the eight radix passes, and nothing but the keys is read.
 // Weights must be non-negative here (degrees); the labels are those of the sorted path.
-typedef unsigned __int128 u128;
-constexpr int SEL_MAX_SPLITS = 1024;
-constexpr int64_t SEL_HIST_BYTES = 4ll << 20;  // per buffer (two buffers)
-
-struct SelSplit {           // one per split point and level parity
-    unsigned long long pre_hi, pre_lo;  // C >> (bits not yet decided)
-    long long residual;                 // weight still to cover among the atoms that share the prefix
-    int dead;                           // its threshold lies beyond the total weight: no atom reaches it
-    int pad;
-};
-
-__device__ __forceinline__ u128 sel_prefix(const SelSplit& s) { return ((u128)s.pre_hi << 64) | (u128)s.pre_lo; }
 
 // Distinct prefixes of the live split points (they are non-decreasing) into glist (loaded by the whole
 // block, compacted in place).  All threads of the block call this; returns the number of groups.
@@ -393,7 +382,7 @@ __device__ int sel_warp_cross(const unsigned long long* p, int count, long long 
 // threshold is crossed.  gid: group of every split point at this level (not read at level 0).
 __device__ void sel_pick_warp(int s, const SelSplit* __restrict__ st_in, SelSplit* __restrict__ st_out, const int* gid,
                               int nsplit, int level, int width, int dbits, int64_t n, int64_t W, int weighted,
-                              const unsigned long long* hist)
+                              const long long* thresholds, const unsigned long long* hist)
 {
     const int lane = threadIdx.x & 31;
     SelSplit me;
@@ -420,7 +409,9 @@ __device__ void sel_pick_warp(int s, const SelSplit* __restrict__ st_in, SelSpli
         sel_warp_cross(coarse, nc, 0x7fffffffffffffffll, &before_c, &total);
         const long long p = s + 1;
         long long T;
-        if (weighted) {
+        if (thresholds != nullptr) {
+            T = thresholds[s];
+        } else if (weighted) {
             T = (total > 0) ? (long long)(((u128)p * (u128)total + (u128)(W - 1)) / (u128)W) : total + 1;
             if (T < 1) T = 1;
         } else {
@@ -457,9 +448,14 @@ __device__ void sel_pick_warp(int s, const SelSplit* __restrict__ st_in, SelSpli
 __global__ void __launch_bounds__(256)
 sel_hist_kernel(const uint64_t* __restrict__ keys, const int64_t* __restrict__ weights, int64_t n, int idx_bits,
                 int shift, int width, int dbits, const SelSplit* __restrict__ st, SelSplit* __restrict__ st_out, int nsplit,
-                int level, int64_t W, unsigned long long* __restrict__ hist, unsigned long long* __restrict__ hist_next,
-                int64_t table_words, unsigned int* __restrict__ done_counter)
+                int level, int64_t W, const long long* __restrict__ thresholds, unsigned long long* __restrict__ hist,
+                unsigned long long* __restrict__ hist_next, int64_t table_words, unsigned int* __restrict__ done_counter,
+                int fine_private)
 {
+    // fine_private (first level, unit weights, width <= 14 only): the digit counters of this block are kept in
+    // shared memory and added to the table once at the end -- for keys that crowd into a few digits (the
+    // ordered bits of float coordinates) a million atomics on a handful of addresses took 90-150 us
+    extern __shared__ unsigned int s_fine[];
     __shared__ u128 glist[SEL_MAX_SPLITS];
     __shared__ int gid[SEL_MAX_SPLITS];
     __shared__ unsigned long long s_coarse[256];
@@ -473,28 +469,49 @@ sel_hist_kernel(const uint64_t* __restrict__ keys, const int64_t* __restrict__ w
     if (level == 0) {
         if (threadIdx.x == 0) glist[0] = 0;
         s_coarse[threadIdx.x] = 0ull;  // one group, every atom counts: coarse counters through shared memory
+        if (fine_private)
+            for (int k = threadIdx.x; k < (1 << width); k += blockDim.x) s_fine[k] = 0u;
         __syncthreads();
     } else {
         ng = sel_groups(st, nsplit, glist, gid);
     }
     const u128 dmask = ((u128)1 << width) - 1;
     if (ng > 0) {
-        for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-            const u128 C = ((u128)keys[i] << idx_bits) | (u128)(uint64_t)i;
-            const u128 P = C >> (shift + width);
-            int lo = 0, hi = ng;  // first group with prefix >= P
-            while (lo < hi) {
-                const int mid = (lo + hi) >> 1;
-                if (glist[mid] < P) lo = mid + 1; else hi = mid;
-            }
-            if (lo < ng && glist[lo] == P) {
-                const unsigned long long w = weights ? (unsigned long long)weights[i] : 1ull;
-                if (w) {
-                    const unsigned digit = (unsigned)((C >> shift) & dmask);
-                    atomicAdd(&hist[((size_t)lo << dbits) + digit], w);
-                    if (level == 0) atomicAdd(&s_coarse[digit >> fbits], w);
-                    else atomicAdd(&coarse[((size_t)lo << 8) + (digit >> fbits)], w);
+        // warp-uniform trip count (all 32 lanes take part in the vote below); lanes past the end carry no counter
+        const int64_t warp_base = (int64_t)blockIdx.x * blockDim.x + (threadIdx.x & ~31);
+        for (int64_t base = warp_base; base < n; base += (int64_t)gridDim.x * blockDim.x) {
+            const int64_t i = base + (threadIdx.x & 31);
+            unsigned long long w = 0ull;
+            size_t slot = ~(size_t)0;  // counter of this atom, or none
+            unsigned digit = 0;
+            int lo = 0;
+            if (i < n) {
+                const u128 C = ((u128)keys[i] << idx_bits) | (u128)(uint64_t)i;
+                const u128 P = C >> (shift + width);
+                int hi = ng;  // first group with prefix >= P
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (glist[mid] < P) lo = mid + 1; else hi = mid;
                 }
+                if (lo < ng && glist[lo] == P) {
+                    w = weights ? (unsigned long long)weights[i] : 1ull;
+                    if (w) {
+                        digit = (unsigned)((C >> shift) & dmask);
+                        slot = ((size_t)lo << dbits) + digit;
+                    }
+                }
+            }
+            if (fine_private) {
+                // crowded keys: lanes that hit the same counter send one atomic between them
+                const unsigned peers = __match_any_sync(0xffffffffu, (unsigned long long)slot);
+                if (slot != ~(size_t)0 && (threadIdx.x & 31) == __ffs((int)peers) - 1) w = (unsigned long long)__popc(peers);
+                else w = 0ull;
+            }
+            if (w) {
+                if (fine_private) atomicAdd(&s_fine[digit], (unsigned int)w);
+                else atomicAdd(&hist[slot], w);
+                if (level == 0) atomicAdd(&s_coarse[digit >> fbits], w);
+                else atomicAdd(&coarse[((size_t)lo << 8) + (digit >> fbits)], w);
             }
         }
     }
@@ -502,6 +519,11 @@ sel_hist_kernel(const uint64_t* __restrict__ keys, const int64_t* __restrict__ w
         __syncthreads();
         const unsigned long long v = s_coarse[threadIdx.x];
         if (v) atomicAdd(&coarse[threadIdx.x], v);
+        if (fine_private)
+            for (int k = threadIdx.x; k < (1 << width); k += blockDim.x) {
+                const unsigned int c = s_fine[k];
+                if (c) atomicAdd(&hist[k], (unsigned long long)c);
+            }
     }
     if (done_counter == nullptr) return;
     __threadfence();
@@ -511,19 +533,20 @@ sel_hist_kernel(const uint64_t* __restrict__ keys, const int64_t* __restrict__ w
     if (!s_last) return;
     __threadfence();
     for (int s = threadIdx.x >> 5; s < nsplit; s += (int)(blockDim.x >> 5))
-        sel_pick_warp(s, st, st_out, gid, nsplit, level, width, dbits, n, W, weights != nullptr ? 1 : 0, hist);
+        sel_pick_warp(s, st, st_out, gid, nsplit, level, width, dbits, n, W, weights != nullptr ? 1 : 0, thresholds, hist);
 }
 
 // the same step as its own launch, eight split points per block (many split points)
 __global__ void __launch_bounds__(256)
 sel_pick_kernel(const SelSplit* __restrict__ st_in, SelSplit* __restrict__ st_out, int nsplit, int level, int width, int dbits,
-                int64_t n, int64_t W, int weighted, const unsigned long long* __restrict__ hist)
+                int64_t n, int64_t W, int weighted, const long long* __restrict__ thresholds,
+                const unsigned long long* __restrict__ hist)
 {
     __shared__ u128 glist[SEL_MAX_SPLITS];
     __shared__ int gid[SEL_MAX_SPLITS];
     if (level > 0) sel_groups(st_in, nsplit, glist, gid);
     const int s = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (s < nsplit) sel_pick_warp(s, st_in, st_out, gid, nsplit, level, width, dbits, n, W, weighted, hist);
+    if (s < nsplit) sel_pick_warp(s, st_in, st_out, gid, nsplit, level, width, dbits, n, W, weighted, thresholds, hist);
 }
 
 __global__ void __launch_bounds__(256)
@@ -554,13 +577,56 @@ sel_label_kernel(const uint64_t* __restrict__ keys, int64_t n, int idx_bits, con
 
 // digit width: the widest the table budget allows for W - 1 groups, then narrowed while the number
 // of levels stays the same (a narrower digit means a smaller table to clear per level)
-static int sel_digit_bits(int64_t W, int total_bits)
+static int sel_digit_bits(int64_t groups, int total_bits)
 {
     int d = 16;
-    while (d > 8 && (int64_t)(W - 1) * (((int64_t)8 << d) + 2048) + 256 > SEL_HIST_BYTES) d--;
+    while (d > 8 && groups * (((int64_t)8 << d) + 2048) + 256 > SEL_HIST_BYTES) d--;
     const int levels = (total_bits + d - 1) / d;
     while (d > 8 && (total_bits + (d - 1) - 1) / (d - 1) == levels) d--;
     return d;
+}
+
+int sel_select_splits(const uint64_t* keys, int key_bits, const int64_t* weights_dev, int64_t n, int nsplit, int64_t W,
+                      const long long* thresholds_dev, unsigned char* state_ws, unsigned char* hist_ws, int* idx_bits_out,
+                      const SelSplit** final_out, bool crowded_keys, cudaStream_t s)
+{
+    if (nsplit < 1 || nsplit > SEL_MAX_SPLITS) return fail_arg("number of split points out of range");
+    int idx_bits = 1;
+    while (idx_bits < 32 && ((int64_t)1 << idx_bits) < n) idx_bits++;
+    const int B = key_bits + idx_bits;
+    const int dbits = sel_digit_bits(nsplit, B);
+    const int levels = (B + dbits - 1) / dbits;
+    SelSplit* st = reinterpret_cast<SelSplit*>(state_ws);
+    unsigned long long* hist = reinterpret_cast<unsigned long long*>(hist_ws);
+    const int64_t hist_words = SEL_HIST_BYTES / 8;
+    const int64_t table_words = ((int64_t)nsplit << dbits) + ((int64_t)nsplit << 8);  // digit + coarse counters of a level
+    // the first table and, behind it, one arrival counter per level
+    unsigned int* counters = reinterpret_cast<unsigned int*>(hist + table_words);
+    DYNB_CUDA_OK(cudaMemsetAsync(hist, 0, (size_t)table_words * 8 + 256, s));
+    const bool fused = nsplit <= 16;  // two rounds of eight warps in the last block
+    const int hgrid = (int)std::min<int64_t>((n + 255) / 256, (int64_t)sm_count_cached() * 4);  // one wave
+    for (int l = 0; l < levels; l++) {
+        const int width = std::min(dbits, B - l * dbits);
+        const int shift = B - l * dbits - width;
+        const SelSplit* st_in = st + (size_t)(l & 1) * SEL_MAX_SPLITS;
+        SelSplit* st_out = st + (size_t)((l + 1) & 1) * SEL_MAX_SPLITS;
+        unsigned long long* h_cur = hist + (size_t)(l & 1) * hist_words;
+        unsigned long long* h_other = hist + (size_t)((l + 1) & 1) * hist_words;
+        unsigned int* done = fused ? counters + l : nullptr;
+        const int priv = (crowded_keys && l == 0 && weights_dev == nullptr && width <= 14) ? 1 : 0;
+        const size_t dyn = priv ? ((size_t)4 << width) : 0;
+        // static + dynamic shared memory beyond 48 KB needs the opt-in
+        if (dyn > 0) DYNB_CUDA_OK(cudaFuncSetAttribute(sel_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        sel_hist_kernel<<<hgrid, 256, dyn, s>>>(keys, weights_dev, n, idx_bits, shift, width, dbits, st_in, st_out, nsplit, l, W,
+                                                thresholds_dev, h_cur, h_other, table_words, done, priv);
+        if (!fused)
+            sel_pick_kernel<<<(nsplit + 7) / 8, 256, 0, s>>>(st_in, st_out, nsplit, l, width, dbits, n, W,
+                                                             weights_dev != nullptr ? 1 : 0, thresholds_dev, h_cur);
+    }
+    DYNB_CUDA_OK(cudaGetLastError());
+    *idx_bits_out = idx_bits;
+    *final_out = st + (size_t)(levels & 1) * SEL_MAX_SPLITS;
+    return DYNB_OK;
 }
 
 struct SfcLayout { int64_t bounds, keys, idx, sorted_w, excl, total_w, sums, rs, total_sort, sel_state, sel_hist, total; };
@@ -650,35 +716,13 @@ extern "C" int dynb_sfc_partition(const float* pos_dev, int64_t n_atoms, const i
         int rc = sfc_keys_into(pos_dev, n_atoms, curve_type, ws, L, keys, nullptr, s);
         if (rc) return rc;
         const int nsplit = (int)(W - 1);
-        int idx_bits = 1;
-        while (idx_bits < 32 && ((int64_t)1 << idx_bits) < n_atoms) idx_bits++;
-        const int B = (curve_type == 0 ? 63 : 21) + idx_bits;
-        const int dbits = sel_digit_bits(W, B);
-        const int levels = (B + dbits - 1) / dbits;
-        SelSplit* st = reinterpret_cast<SelSplit*>(ws + L.sel_state);
-        unsigned long long* hist = reinterpret_cast<unsigned long long*>(ws + L.sel_hist);
-        const int64_t hist_words = SEL_HIST_BYTES / 8;
-        const int64_t table_words = ((int64_t)nsplit << dbits) + ((int64_t)nsplit << 8);  // digit + coarse counters of a level
-        // the first table and, behind it, one arrival counter per level
-        unsigned int* counters = reinterpret_cast<unsigned int*>(hist + table_words);
-        DYNB_CUDA_OK(cudaMemsetAsync(hist, 0, (size_t)table_words * 8 + 256, s));
-        const bool fused = nsplit <= 16;  // two rounds of eight warps in the last block
-        const int hgrid = (int)std::min<int64_t>((n_atoms + 255) / 256, (int64_t)sm_count_cached() * 4);  // one wave
-        for (int l = 0; l < levels; l++) {
-            const int width = std::min(dbits, B - l * dbits);
-            const int shift = B - l * dbits - width;
-            const SelSplit* st_in = st + (size_t)(l & 1) * SEL_MAX_SPLITS;
-            SelSplit* st_out = st + (size_t)((l + 1) & 1) * SEL_MAX_SPLITS;
-            unsigned long long* h_cur = hist + (size_t)(l & 1) * hist_words;
-            unsigned long long* h_other = hist + (size_t)((l + 1) & 1) * hist_words;
-            unsigned int* done = fused ? counters + l : nullptr;
-            sel_hist_kernel<<<hgrid, 256, 0, s>>>(keys, weights_dev, n_atoms, idx_bits, shift, width, dbits, st_in, st_out, nsplit, l, W,
-                                                  h_cur, h_other, table_words, done);
-            if (!fused)
-                sel_pick_kernel<<<(nsplit + 7) / 8, 256, 0, s>>>(st_in, st_out, nsplit, l, width, dbits, n_atoms, W,
-                                                                 weights_dev != nullptr ? 1 : 0, h_cur);
-        }
-        sel_label_kernel<<<hgrid, 256, 0, s>>>(keys, n_atoms, idx_bits, st + (size_t)(levels & 1) * SEL_MAX_SPLITS, nsplit, labels_dev);
+        int idx_bits = 0;
+        const SelSplit* splits = nullptr;
+        rc = sel_select_splits(keys, curve_type == 0 ? 63 : 21, weights_dev, n_atoms, nsplit, W, nullptr, ws + L.sel_state, ws + L.sel_hist,
+                               &idx_bits, &splits, false, s);
+        if (rc) return rc;
+        const int hgrid = (int)std::min<int64_t>((n_atoms + 255) / 256, (int64_t)sm_count_cached() * 4);
+        sel_label_kernel<<<hgrid, 256, 0, s>>>(keys, n_atoms, idx_bits, splits, nsplit, labels_dev);
         DYNB_CUDA_OK(cudaGetLastError());
         return DYNB_OK;
     }
