@@ -20,9 +20,11 @@ from .exchange import (  # noqa: F401
     FeatureExchanger,
     FeaturePushToExchange,
     GPUDirectExchanger,
+    IPCExchanger,
     PythonNCCLExchanger,
     drift_flags,
     push_buffer_create,
+    supports_fabric_handles,
 )
 from .halo import extract_halo_info, filter_edges_to_radius  # noqa: F401
 from .partition import (  # noqa: F401

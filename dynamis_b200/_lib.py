@@ -24,6 +24,7 @@ _p = ctypes.c_void_p
 _i64 = ctypes.c_int64
 _i32 = ctypes.c_int
 _f64 = ctypes.c_double
+_u32 = ctypes.c_uint32
 
 
 class RgHeader(ctypes.Structure):
@@ -36,6 +37,40 @@ class RgHeader(ctypes.Structure):
         ("group_cells", ctypes.c_int32),
         ("num_groups", ctypes.c_int64),
         ("reserved", ctypes.c_int64 * 2),
+    ]
+
+
+class HaloPeer(ctypes.Structure):
+    """dynb_halo_peer"""
+    _fields_ = [
+        ("remote_base", ctypes.c_void_p),
+        ("flags_off", ctypes.c_int64),
+        ("fwd_ring_tail", ctypes.c_int64),
+        ("fwd_ring_stride", ctypes.c_int64),
+        ("fwd_stage_off", ctypes.c_int64 * 2),
+        ("fwd_row_offset", ctypes.c_int64),
+        ("send_start", ctypes.c_int64),
+        ("send_count", ctypes.c_int64),
+        ("bwd_off", ctypes.c_int64 * 2),
+        ("bwd_row_offset", ctypes.c_int64),
+        ("recv_start", ctypes.c_int64),
+        ("recv_count", ctypes.c_int64),
+    ]
+
+
+class HaloCtx(ctypes.Structure):
+    """dynb_halo_ctx"""
+    _fields_ = [
+        ("peers", ctypes.c_void_p),
+        ("local_base", ctypes.c_void_p),
+        ("local_flags_off", ctypes.c_int64),
+        ("done_counter", ctypes.c_void_p),
+        ("drift_local", ctypes.c_void_p),
+        ("drift_global", ctypes.c_void_p),
+        ("status_dev", ctypes.c_void_p),
+        ("status_host", ctypes.c_void_p),
+        ("world_size", ctypes.c_int32),
+        ("rank", ctypes.c_int32),
     ]
 
 
@@ -66,13 +101,18 @@ SIGNATURES = {
     "dynb_filter_edges_plan": (_i32, [_p, _p, _p, _p, _f64, _i64, _p, _p, _i64, _p]),
     "dynb_filter_edges_fill": (_i32, [_p, _p, _i32, _i64, _i64, _p, _p, _p, _p]),
     "dynb_pack_rows": (_i32, [_p, _i64, _i64, _p, _i64, _p, _p, _p]),
-    "dynb_push_rows": (_i32, [_p, _i64, _p, _i64, _p, _i32, _i64, _i32, _p]),
-    "dynb_signal_peers": (_i32, [_p, _i32, ctypes.c_uint32, _p]),
-    "dynb_wait_flags": (_i32, [_p, _p, _i32, ctypes.c_uint32, _i64, _p, _p]),
+    "dynb_push_rows": (_i32, [_p, _i64, _i64, _p, _i64, _p, _i32, _i64, _i32, _p, _p]),
+    "dynb_halo_forward_begin": (_i32, [_p, _p, _i64, _i64, _p, _i64, _p, _u32, _u32, _i32, _p]),
+    "dynb_halo_forward_end": (_i32, [_p, _u32, _i64, _p, _p, _i64, _p]),
+    "dynb_halo_backward_begin": (_i32, [_p, _p, _i64, _i64, _i64, _p, _p, _u32, _p]),
+    "dynb_halo_backward_end": (_i32, [_p, _u32, _i64, _p, _p, _i64, _i64, _i32, _p, _p, _p, _p, _p]),
+    "dynb_halo_signal": (_i32, [_p, _i32, _u32, _u32, _p]),
+    "dynb_halo_wait": (_i32, [_p, _i32, _u32, _i64, _p]),
+    "dynb_host_alloc_mapped": (_i32, [_i64, ctypes.POINTER(_p), ctypes.POINTER(_p)]),
+    "dynb_host_free_mapped": (_i32, [_p]),
     "dynb_inverse_csr_workspace_bytes": (_i32, [_i64, _i64, ctypes.POINTER(_i64)]),
     "dynb_inverse_csr": (_i32, [_p, _i64, _i64, _p, _p, _p, _p, _i64, _p]),
     "dynb_unpack_add_rows": (_i32, [_p, _i64, _i64, _i32, _p, _p, _p, _p, _p]),
-    "dynb_add_rows_listed": (_i32, [_p, _i64, _i64, _i32, _p, _p, _p, _p, _p]),
     "dynb_ipc_alloc": (_i32, [_i64, ctypes.POINTER(_p)]),
     "dynb_ipc_free": (_i32, [_p]),
     "dynb_ipc_export": (_i32, [_p, _p]),
@@ -83,7 +123,7 @@ SIGNATURES = {
     "dynb_scatter_rows": (_i32, [_p, _i64, _p, _i64, _i64, _p, _p, _p]),
     "dynb_drift_flag": (_i32, [_p, _p, _p, _p, _i64, _f64, _f64, _p, _p, _p]),
     "dynb_kdtree_workspace_bytes": (_i32, [_i64, _i64, ctypes.POINTER(_i64)]),
-    "dynb_kdtree_partition": (_i32, [_p, _i64, _p, _i64, _p, _p, _i64, _p]),
+    "dynb_kdtree_partition": (_i32, [_p, _i64, _p, _i64, _p, _i32, _p, _i64, _p]),
     "dynb_integrator_step": (_i32, [_i32, _p, _p, _p, _p, _p, _i64, _f64, _f64, _f64, _p, _p, _f64, _p, _p, _p]),
     "dynb_sfc_static_max_atoms": (_i64, []),
     "dynb_sfc_partition_static": (_i32, [_p, _i64, _p, _i64, _i32, _p, _p, _p]),

@@ -224,9 +224,10 @@ extern "C" int dynb_kdtree_workspace_bytes(int64_t n_atoms, int64_t W, int64_t* 
 }
 
 extern "C" int dynb_kdtree_partition(const float* pos_dev, int64_t n_atoms, const int64_t* weights_dev, int64_t W,
-                                     int64_t* labels_dev, void* workspace_dev, int64_t workspace_bytes, void* stream)
+                                     int64_t* labels_dev, int method, void* workspace_dev, int64_t workspace_bytes, void* stream)
 {
     if (n_atoms < 0) return fail_arg("n_atoms must be non-negative");
+    if (method != 0 && method != 1) return fail_arg("method must be 0 (automatic) or 1 (sorted cuts)");
     if (W < 1 || W > (1ll << 20)) return fail_arg("W must be >= 1");
     if (n_atoms == 0) return DYNB_OK;
     if (pos_dev == nullptr || labels_dev == nullptr) return fail_arg("null pointer");
@@ -254,7 +255,7 @@ extern "C" int dynb_kdtree_partition(const float* pos_dev, int64_t n_atoms, cons
     long long* start = reinterpret_cast<long long*>(ws + L.start);
     long long* mid = reinterpret_cast<long long*>(ws + L.mid);
     long long* thr = reinterpret_cast<long long*>(ws + L.thr);
-    const bool by_selection = (weights_dev == nullptr) && W <= SEL_MAX_SPLITS && getenv("DYNB_KD_SORT") == nullptr;  // env: testing knob
+    const bool by_selection = (weights_dev == nullptr) && W <= SEL_MAX_SPLITS && method == 0;
     uint32_t* box = reinterpret_cast<uint32_t*>(ws + L.box);
     int64_t* base_label = reinterpret_cast<int64_t*>(ws + L.base_label);
     int64_t rs_bytes = 0;

@@ -1128,15 +1128,7 @@ __global__ void rg_zero_counts_kernel(int64_t Nt, int32_t* counts_out)
 // ------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------
-static int pair_grid_waves()
-{
-    static const int waves = [] {
-        int w = PAIR_GRID_WAVES;
-        if (const char* env = getenv("DYNB_RG_WAVES")) w = atoi(env);  // tuning knob
-        return std::min(std::max(w, 1), 64);
-    }();
-    return waves;
-}
+static int pair_grid_waves() { return PAIR_GRID_WAVES; }
 
 struct RgLayout {
     int64_t hdr, partials, tpartials, posw, aff, ccount, cfill, tccount, tcfill, skey, scell, spos, scode, smeta, hitmask, tkey, tcell, tpos, tmeta,
@@ -1322,11 +1314,7 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
     const int vec_ok = (reinterpret_cast<uintptr_t>(pos_dev) % 16 == 0) ? 1 : 0;
     rg_wrap_kernel<T><<<(unsigned)((N + WRAP_THREADS - 1) / WRAP_THREADS), WRAP_THREADS, 0, stream>>>(
         static_cast<const T*>(pos_dev), N, g, vec_ok, posw, aff, h, reinterpret_cast<unsigned long long*>(w + L.partials));
-    // tuning knob: DYNB_RG_GROUP="sx,sy" forces the cells per warp work item (default: chosen on the device)
-    int force_sx = 0, force_sy = 0;
-    if (const char* env = getenv("DYNB_RG_GROUP")) sscanf(env, "%d,%d", &force_sx, &force_sy);
-    if (force_sx < 0 || force_sx > 8) force_sx = 0;
-    if (force_sy < 0 || force_sy > 2) force_sy = 0;
+    const int force_sx = 0, force_sy = 0;  // cells per warp work item: chosen on the device
     int n_tpart = 0;
     if (targets != nullptr) {
         n_tpart = (int)((Nt + 255) / 256);

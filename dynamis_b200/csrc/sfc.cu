@@ -653,10 +653,10 @@ static SfcLayout sfc_layout(int64_t n)
 static int sfc_keys_into(const float* pos, int64_t n, int curve, unsigned char* ws, const SfcLayout& L, uint64_t* keys,
                          uint32_t* idx, cudaStream_t stream)
 {
-    SfcBounds init;
-    for (int k = 0; k < 3; k++) { init.mn[k] = 0xffffffffu; init.mx[k] = 0u; init.pmin[k] = 0.f; init.prange[k] = 1.f; }
+    // extrema start at +max / 0 in the ordered-integer image; set on the device (no copy from host memory)
     SfcBounds* b = reinterpret_cast<SfcBounds*>(ws + L.bounds);
-    DYNB_CUDA_OK(cudaMemcpyAsync(b, &init, sizeof(init), cudaMemcpyHostToDevice, stream));
+    DYNB_CUDA_OK(cudaMemsetAsync(b->mn, 0xff, sizeof(b->mn), stream));
+    DYNB_CUDA_OK(cudaMemsetAsync(b->mx, 0, sizeof(SfcBounds) - sizeof(b->mn), stream));
     const int grid = (int)std::min<int64_t>((n + 255) / 256, (int64_t)sm_count_cached() * 4);
     sfc_minmax_kernel<<<grid, 256, 0, stream>>>(pos, n, b);
     const unsigned nbk = (unsigned)((n + 255) / 256);
@@ -710,8 +710,7 @@ extern "C" int dynb_sfc_partition(const float* pos_dev, int64_t n_atoms, const i
     unsigned char* ws = static_cast<unsigned char*>(workspace_dev);
     uint64_t* keys = reinterpret_cast<uint64_t*>(ws + L.keys);
     uint32_t* idx = reinterpret_cast<uint32_t*>(ws + L.idx);
-    static const bool force_sort = getenv("DYNB_SFC_SORT") != nullptr;  // testing knob: always take the sorted path
-    if (perm_dev == nullptr && W >= 2 && W - 1 <= SEL_MAX_SPLITS && workspace_bytes >= L.total && !force_sort) {
+    if (perm_dev == nullptr && W >= 2 && W - 1 <= SEL_MAX_SPLITS && workspace_bytes >= L.total) {
         // labels by selection (no sort)
         int rc = sfc_keys_into(pos_dev, n_atoms, curve_type, ws, L, keys, nullptr, s);
         if (rc) return rc;

@@ -245,9 +245,10 @@ class SFCPartitioner(AbstractPartitioner):
         return info
 
 
-def kdtree_partition_labels(pos: torch.Tensor, weights: Optional[torch.Tensor], W: int) -> torch.Tensor:
+def kdtree_partition_labels(pos: torch.Tensor, weights: Optional[torch.Tensor], W: int, sorted_cuts: bool = False) -> torch.Tensor:
     """Rank label in [0, W) per atom by recursive bisection along the widest axis
-    (reference: kdtree_bisect_cuda, partition/kdtree.cpp:9-26)."""
+    (reference: kdtree_bisect_cuda, partition/kdtree.cpp:9-26).  ``sorted_cuts`` takes the sort-based
+    route also for equal-count cuts (same labels)."""
     if not pos.is_cuda:
         raise RuntimeError("pos must be a CUDA tensor")
     if pos.dim() != 2 or pos.size(1) != 3:
@@ -272,7 +273,8 @@ def kdtree_partition_labels(pos: torch.Tensor, weights: Optional[torch.Tensor], 
             _lib.check(L.dynb_kdtree_workspace_bytes(N, int(W), ctypes.byref(nbytes)), "kdtree_workspace_bytes")
             ws = scratch(dev, "kdtree", nbytes.value)
             _lib.check(L.dynb_kdtree_partition(pos.data_ptr(), N, weights.data_ptr() if weights is not None else None, int(W),
-                                               labels.data_ptr(), ws.data_ptr(), ws.numel(), _stream(dev)), "kdtree_partition")
+                                               labels.data_ptr(), 1 if sorted_cuts else 0, ws.data_ptr(), ws.numel(), _stream(dev)),
+                       "kdtree_partition")
     return labels
 
 

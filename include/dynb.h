@@ -189,32 +189,102 @@ int dynb_pack_rows(const void* input_dev, int64_t n_rows_in, int64_t row_bytes, 
                    void* out_dev, uint32_t* bad_dev, void* stream);
 
 /* One peer segment of a push: rows [start, start + count) of the logical send list are stored
- * into remote_ptr (a peer's mapped buffer) starting at row remote_row_offset.  Same role as the
- * reference's PushTarget (dynamis_model/include/dynamis_model/exchanger.hpp:13-18). */
+ * into remote_ptr (a peer's mapped buffer of remote_rows rows) starting at row remote_row_offset.
+ * Same role as the reference's PushTarget (dynamis_model/include/dynamis_model/exchanger.hpp:13-18). */
 typedef struct dynb_push_target {
     void* remote_ptr;
     int64_t remote_row_offset;
     int64_t start;
     int64_t count;
+    int64_t remote_rows;
 } dynb_push_target;
 
-/* Fused gather + store into peers' memory over NVLink (gather_and_push_kernel and
- * gather_ghost_grad_and_push_kernel, dynamis_model/src/csrc/exchange/ipc_exchange_kernels.cu:40-122).
+/* Gather + store into peers' memory over NVLink, as a stand-alone launch: IPCExchanger::push_forward /
+ * push_backward (gather_and_push_kernel and gather_ghost_grad_and_push_kernel,
+ * dynamis_model/src/csrc/exchange/ipc_exchange_kernels.cu:40-122).
  * row_index_dev != NULL: logical row i is x[row_index_dev[i]] (forward push of send_local_indices);
  * NULL: logical row i is x[src_row_base + i] (backward push of the contiguous ghost rows).
- * remote_align: guaranteed byte alignment of every remote row start (16 when the remote buffers
- * and row_bytes are 16-byte multiples). */
-int dynb_push_rows(const void* x_dev, int64_t row_bytes, const int64_t* row_index_dev, int64_t src_row_base,
-                   const dynb_push_target* targets_dev, int n_targets, int64_t total_rows, int remote_align, void* stream);
+ * x has n_rows_in rows.  remote_align: guaranteed byte alignment of every remote row start (16 when the
+ * remote buffers and row_bytes are 16-byte multiples).  A row whose source lies outside x or whose
+ * destination lies outside the target's remote_rows is skipped and *bad_dev (optional uint32) set. */
+int dynb_push_rows(const void* x_dev, int64_t n_rows_in, int64_t row_bytes, const int64_t* row_index_dev,
+                   int64_t src_row_base, const dynb_push_target* targets_dev, int n_targets, int64_t total_rows,
+                   int remote_align, uint32_t* bad_dev, void* stream);
 
-/* Generation signalling (record_push_complete / wait_for_pushes,
- * dynamis_model/src/csrc/exchange/ipc_exchanger.cpp:784-828).  dynb_signal_peers release-stores
- * `value` into each non-NULL remote flag; dynb_wait_flags waits until flags_dev[k] >= value for every k
- * with expect_dev[k] != 0 (all k when expect_dev is NULL), for at most timeout_ns; on expiry
- * *status_dev becomes 1 + k of a flag that never arrived (0 = all arrived) and the kernel returns. */
-int dynb_signal_peers(uint32_t* const* remote_flag_ptrs_dev, int n, uint32_t value, void* stream);
-int dynb_wait_flags(const uint32_t* flags_dev, const uint8_t* expect_dev, int n, uint32_t value, int64_t timeout_ns,
-                    uint32_t* status_dev, void* stream);
+/* ---- fused halo exchange (FeatureExchanger::feature_push_forward / feature_push_backward,
+ * dynamis_model/src/csrc/exchanger.cu:48-120, over IPCExchanger::push_forward / push_backward /
+ * record_push_complete / wait_for_pushes, dynamis_model/src/csrc/exchange/ipc_exchanger.cpp:517-828).
+ *
+ * Every rank owns ONE peer-visible allocation ("exchange allocation") that holds
+ *   - result slots [n_local + n_ghost rows] into whose tail the peers store this rank's ghost rows
+ *     directly (optional: ring of fwd_ring slots), two staging ghost buffers used when no slot is free,
+ *   - two gradient receive buffers [total_send rows] (generation parity),
+ *   - handshake records: for each direction (0 forward, 1 reverse, 2 bare handshake), generation
+ *     parity and sender a 16-byte record {generation, announced slot, drift word, pad}.
+ * A peer only ever receives stores.  Per direction the g-th call of every rank forms generation g; all
+ * ranks must issue the same sequence of calls.
+ *
+ * dynb_halo_peer describes rank k as seen from this rank (entry `rank` itself: remote_base NULL). */
+typedef struct dynb_halo_peer {
+    void* remote_base;        /* peer's exchange allocation mapped into this process, NULL = not a peer */
+    int64_t flags_off;        /* byte offset of the handshake records inside the peer's allocation */
+    int64_t fwd_ring_tail;    /* byte offset of the ghost tail of the peer's result slot 0 */
+    int64_t fwd_ring_stride;  /* bytes between consecutive result slots of the peer */
+    int64_t fwd_stage_off[2]; /* byte offsets of the peer's two staging ghost buffers (generation parity) */
+    int64_t fwd_row_offset;   /* first row of this rank's segment inside the peer's ghost region */
+    int64_t send_start;       /* segment of this rank's send list that goes to the peer */
+    int64_t send_count;
+    int64_t bwd_off[2];       /* byte offsets of the peer's two gradient receive buffers */
+    int64_t bwd_row_offset;   /* first row of this rank's segment inside the peer's receive buffer */
+    int64_t recv_start;       /* segment of this rank's ghost rows owned by the peer */
+    int64_t recv_count;
+} dynb_halo_peer;
+
+typedef struct dynb_halo_ctx {
+    const dynb_halo_peer* peers;  /* device array [world_size] */
+    void* local_base;             /* this rank's exchange allocation */
+    int64_t local_flags_off;
+    uint32_t* done_counter;       /* device word, zero between launches */
+    const int32_t* drift_local;   /* device int32 attached to every signal, or NULL (set_watchdog_flags) */
+    int32_t* drift_global;        /* device int32 <- OR over all ranks' words after every wait, or NULL */
+    uint32_t* status_dev;         /* two device words: [0] 1 + rank whose signal never arrived, [1] bad row index */
+    uint32_t* status_host;        /* the same two words in mapped host memory (device address), or NULL */
+    int32_t world_size;
+    int32_t rank;
+} dynb_halo_ctx;
+
+/* Forward, first half (one launch): send-list rows -> peers' ghost regions; x[0:n_local] -> out_head
+ * (NULL: no local copy); then the generation signal, carrying announce_slot (0 = "store my next ghost
+ * rows into my staging buffer", s + 1 = "into my result slot s") and the drift word.  The destination of
+ * this generation's rows is what each peer announced with its previous signal.  skip_push != 0: the rows
+ * were delivered by other means (copy engine) before this call; only copy and signal. */
+int dynb_halo_forward_begin(const dynb_halo_ctx* ctx, const void* x_dev, int64_t n_local, int64_t row_bytes,
+                            const int64_t* send_local_dev, int64_t total_send, void* out_head_dev, uint32_t gen,
+                            uint32_t announce_slot, int skip_push, void* stream);
+/* Forward, second half (one launch): waits at most timeout_ns for every peer's signal of `gen`, ORs the
+ * drift words into drift_global, and copies stage_dev -> out_tail_dev when the rows arrived in staging
+ * (out_tail_dev NULL: they are already in place).  On expiry the status words are set and the kernel
+ * returns. */
+int dynb_halo_forward_end(const dynb_halo_ctx* ctx, uint32_t gen, int64_t timeout_ns, const void* stage_dev,
+                          void* out_tail_dev, int64_t tail_bytes, void* stream);
+/* Reverse, first half: grad rows [n_local, n_local + n_ghost) -> their owners' receive buffers;
+ * grad[0:n_local] -> out (rows with has_recv_dev[row] != 0 may be left to the second half); signal. */
+int dynb_halo_backward_begin(const dynb_halo_ctx* ctx, const void* grad_dev, int64_t n_local, int64_t n_ghost,
+                             int64_t row_bytes, const uint8_t* has_recv_dev, void* out_dev, uint32_t gen, void* stream);
+/* Reverse, second half: bounded wait, drift OR, then out[row] = grad[row] + the received rows naming row
+ * (inverse CSR of dynb_inverse_csr, fixed order, no atomics) for the n_rows rows listed in rows_dev. */
+int dynb_halo_backward_end(const dynb_halo_ctx* ctx, uint32_t gen, int64_t timeout_ns, const void* grad_dev,
+                           const int64_t* rows_dev, int64_t n_rows, int64_t feature_dim, int dtype, const void* recv_dev,
+                           const int64_t* inv_offsets_dev, const uint32_t* inv_entries_dev, void* out_dev, void* stream);
+/* A handshake without rows (record_push_complete / wait_for_pushes as stand-alone calls,
+ * ipc_exchanger.cpp:784-828): the signal carries the drift word (flag copied before the counter write,
+ * :788-796), the wait ORs all ranks' words into drift_global (watchdog_or_kernel,
+ * ipc_exchange_kernels.cu:234-253 — there by remote loads, here from records the peers stored). */
+int dynb_halo_signal(const dynb_halo_ctx* ctx, int direction, uint32_t gen, uint32_t announce_slot, void* stream);
+int dynb_halo_wait(const dynb_halo_ctx* ctx, int direction, uint32_t gen, int64_t timeout_ns, void* stream);
+/* Page-locked host words that kernels can store to (the status words above), and their release. */
+int dynb_host_alloc_mapped(int64_t bytes, void** host_ptr_out, void** dev_ptr_out);
+int dynb_host_free_mapped(void* host_ptr);
 
 /* Reverse halo: out[i, :] = grad[i, :] + sum of the received rows that name local row i, in fixed
  * peer order (replaces clone + index_add_, dynamis_model/src/csrc/exchanger.cu:111-117, which
@@ -226,16 +296,10 @@ int dynb_inverse_csr(const int64_t* send_local_dev, int64_t total_send, int64_t 
                      void* stream);
 int dynb_unpack_add_rows(const void* grad_dev, int64_t n_local, int64_t feature_dim, int dtype, const void* recv_dev,
                          const int64_t* inv_offsets_dev, const uint32_t* inv_entries_dev, void* out_dev, void* stream);
-/* The same accumulation in two steps, so that the copy of the local gradient rows can run while the
- * peers' rows are still arriving: the caller copies grad[0:n_local] into out_dev, waits for the rows, and
- * this call adds the received rows to the n_rows local rows listed in rows_dev (those named by at least
- * one send entry), in the same order as dynb_unpack_add_rows — the result is bit-identical. */
-int dynb_add_rows_listed(const int64_t* rows_dev, int64_t n_rows, int64_t feature_dim, int dtype, const void* recv_dev,
-                         const int64_t* inv_offsets_dev, const uint32_t* inv_entries_dev, void* out_dev, void* stream);
-
 /* Peer-visible memory (allocate_ipc_buffer / export_ipc_handle / cudaIpcOpenMemHandle,
- * dynamis_model/src/csrc/exchange/ipc_exchanger.cpp:117-252, 406-430).  These are the only calls of
- * the library that allocate, free or map device memory; dynb_ipc_alloc zero-fills and synchronises. */
+ * dynamis_model/src/csrc/exchange/ipc_exchanger.cpp:117-252, 406-430).  These and
+ * dynb_host_alloc_mapped are the only calls of the library that allocate, free or map memory;
+ * dynb_ipc_alloc zero-fills and synchronises. */
 int dynb_ipc_alloc(int64_t bytes, void** ptr_out);
 int dynb_ipc_free(void* ptr);
 int dynb_ipc_export(void* ptr, uint8_t* handle64_out);
@@ -263,10 +327,12 @@ int dynb_drift_flag(const float* cur_dev, const float* ref_dev, const float* vel
  * kdtree_kernels.cu:264-467): labels_dev[i] in [0, W) by recursive bisection along the widest axis of
  * each segment, ceil(log2 W) levels.  weights_dev: int64 per-atom cost (non-negative) or NULL (equal
  * counts).  Atoms with equal coordinates are ordered by ascending index; weights are summed exactly
- * (the reference uses a float32 cumulative sum, identical while the sums stay below 2^24). */
+ * (the reference uses a float32 cumulative sum, identical while the sums stay below 2^24).
+ * method 0: equal-count cuts by selection (no sort), weighted cuts by a stable sort; method 1: sorted
+ * cuts for both (same labels; kept so that the two routes can be checked against each other). */
 int dynb_kdtree_workspace_bytes(int64_t n_atoms, int64_t W, int64_t* bytes);
 int dynb_kdtree_partition(const float* pos_dev, int64_t n_atoms, const int64_t* weights_dev, int64_t W,
-                          int64_t* labels_dev, void* workspace_dev, int64_t workspace_bytes, void* stream);
+                          int64_t* labels_dev, int method, void* workspace_dev, int64_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------ integrator steps
  * Replaces EulerIntegrator::step, VerletIntegrator::halfstep1/2 and LangevinIntegrator::halfstep1/2
@@ -290,6 +356,9 @@ int dynb_integrator_step(int kind, float* pos_dev, float* vel_dev, const float* 
  * library image (6 MiB per GPU that loads the library, held until the process exits) instead of a
  * caller-provided workspace.  Limits and rules:
  *   - n_atoms <= dynb_sfc_static_max_atoms() (131072); larger inputs are rejected with DYNB_ERR_ARG.
+ *   - The array is sized for the sorted route of dynb_sfc_partition only, so this entry point always
+ *     sorts (also with perm_dev == NULL, where dynb_sfc_partition with its full workspace would select
+ *     the split points without a sort); the labels are the same either way.
  *   - The call itself allocates and frees nothing (no cudaMalloc / cudaFree, no allocating library
  *     routine); inputs and outputs are the caller's.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with

@@ -1,12 +1,12 @@
 """TEST INFRASTRUCTURE ONLY — compiles the reference's own CUDA sources for the hot path into
 oracle/_ref/libdynamis_ref.so (git-ignored), for use as the parity oracle on a GPU.
 
-The four reference .cu files are compiled where they lie (nothing is copied), with nvcc for
+The reference .cu files of the path (radius graph, SFC, halo ops, KD-tree, integrators) are compiled where they lie (nothing is copied), with nvcc for
 compute_100 exactly as the reference's own CMake does (plain SIMT, default FMA contraction),
 against this image's libtorch headers, together with ref_shim.cpp (ours) which registers them as
 torch ops in the ``dynamis_ref`` namespace.  The reference's build system is not run.
 
-    python oracle/build_ref.py [--reference /root/reference]
+    python oracle/build_ref.py [--reference DIR]      (default: $DYNB_REFERENCE, else /root/reference)
 """
 
 from __future__ import annotations
@@ -23,10 +23,19 @@ REF_SOURCES = [
     "dynamis_state/src/csrc/partition/sfc_kernels.cu",
     "dynamis_state/src/csrc/graph/dist_graph_ops_kernels.cu",
     "dynamis_state/src/csrc/partition/kdtree_kernels.cu",
+    "dynamis_integrator/src/csrc/euler_integrator.cu",
+    "dynamis_integrator/src/csrc/verlet_integrator.cu",
+    "dynamis_integrator/src/csrc/langevin_integrator.cu",
 ]
+SHIMS = ["ref_shim.cpp", "ref_shim_integrators.cpp"]
+DEFAULT_REFERENCE = os.environ.get("DYNB_REFERENCE", "/root/reference")
+
+# What the reference's CMake writes from dynamis_state/include/dynamis_state/timing_config.hpp.in with
+# its timing option OFF (dynamis_state/CMakeLists.txt:17-19): the integrator sources include it.
+TIMING_CONFIG = "#pragma once\n/* #undef DYNAMIS_TIMING */\n"
 
 
-def build(reference: str = "/root/reference", force: bool = False) -> str | None:
+def build(reference: str = DEFAULT_REFERENCE, force: bool = False) -> str | None:
     if not os.path.isdir(reference):
         return SO if os.path.exists(SO) else None
     if os.path.exists(SO) and not force:
@@ -34,8 +43,16 @@ def build(reference: str = "/root/reference", force: bool = False) -> str | None
     import torch
     from torch.utils import cpp_extension as ce
 
-    os.makedirs(OUT, exist_ok=True)
-    inc = [f"-I{p}" for p in ce.include_paths("cuda")] + [f"-I{reference}/dynamis_state/include"]
+    import sysconfig
+
+    gen = os.path.join(OUT, "include", "dynamis_state")
+    os.makedirs(gen, exist_ok=True)
+    with open(os.path.join(gen, "timing_config.hpp"), "w") as f:
+        f.write(TIMING_CONFIG)
+    inc = [f"-I{p}" for p in ce.include_paths("cuda")] + [f"-I{reference}/dynamis_state/include",
+                                                            f"-I{reference}/dynamis_integrator/include",
+                                                            f"-I{os.path.join(OUT, 'include')}",
+                                                            f"-I{sysconfig.get_paths()['include']}"]
     common = ["-std=c++17", "-O2", "-DTORCH_API_INCLUDE_EXTENSION_H", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     objs, procs = [], []
@@ -45,10 +62,11 @@ def build(reference: str = "/root/reference", force: bool = False) -> str | None
                "-ccbin", "/usr/bin/g++", "--expt-relaxed-constexpr", "-c", os.path.join(reference, rel), "-o", o]
         procs.append((rel, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         objs.append(o)
-    o = os.path.join(OUT, "ref_shim.o")
-    cmd = ["/usr/bin/g++", *common, *inc, "-fPIC", "-c", os.path.join(HERE, "ref_shim.cpp"), "-o", o]
-    procs.append(("ref_shim.cpp", subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
-    objs.append(o)
+    for shim in SHIMS:
+        o = os.path.join(OUT, shim[:-4] + ".o")
+        cmd = ["/usr/bin/g++", *common, *inc, "-fPIC", "-c", os.path.join(HERE, shim), "-o", o]
+        procs.append((shim, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+        objs.append(o)
     for rel, p in procs:
         out, _ = p.communicate()
         if p.returncode != 0:
@@ -75,5 +93,5 @@ def load():
 
 
 if __name__ == "__main__":
-    ref = sys.argv[sys.argv.index("--reference") + 1] if "--reference" in sys.argv else "/root/reference"
+    ref = sys.argv[sys.argv.index("--reference") + 1] if "--reference" in sys.argv else DEFAULT_REFERENCE
     print(build(ref, force="--force" in sys.argv))

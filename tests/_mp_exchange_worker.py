@@ -69,6 +69,89 @@ def main():
                 ex.exchanger.check_status()
             dist.barrier()
             ex.reset_buffers()
+    # the drift word rides on the handshake of every push (reference: comm/drift_flags.py,
+    # dynamis/tests/test_drift_watchdog.py:97-120): one rank raises a bit, every rank sees it after the push
+    flags = D.drift_flags.enable(dev)
+    ex = D.GPUDirectExchanger(wait_ns=10_000_000_000)
+    F = 8
+    x = torch.randn(nl[rank], F, device=dev)
+    for it in range(8):
+        word = (1 + (it % 3)) if (it % W == rank and it % 2 == 0) else 0
+        flags.local.fill_(word)
+        out = ex.feature_push_forward(x, info)
+        assert int(flags.global_.item()) == ((1 + (it % 3)) if it % 2 == 0 else 0), f"drift word, generation {it}"
+        flags.local.fill_(2 if rank == W - 1 else 0)
+        ex.feature_push_backward(torch.ones_like(out), x.shape, info)
+        assert int(flags.global_.item()) == 2
+    assert flags.n_wired == 1
+    D.drift_flags.disable(dev)
+    dist.barrier()
+    ex.reset_buffers()
+
+    # the reference's own set-up sequence (comm/exchanger.py:401-536): caller-allocated buffers, handles
+    # gathered over the process group, setup_ipc with 13 arguments, sync handle, setup_sync
+    def gather_bytes(h):
+        lst = [None] * W
+        dist.all_gather_object(lst, list(h))
+        return lst
+
+    total_recv, total_send = int(info.recv_offsets[-1]), int(info.send_offsets[-1])
+    all_ro = [torch.zeros(W + 1, dtype=torch.int64, device=dev) for _ in range(W)]
+    dist.all_gather(all_ro, info.recv_offsets.to(dev))
+    all_ro = torch.stack(all_ro)
+    all_nl = [torch.zeros(1, dtype=torch.int64, device=dev) for _ in range(W)]
+    dist.all_gather(all_nl, torch.tensor([nl[rank]], dtype=torch.int64, device=dev))
+    all_nl = torch.cat(all_nl)
+    frng = np.random.default_rng(4321)
+    feats = [frng.standard_normal((nl[r], F)).astype(np.float32) for r in range(W)]
+    ref = O.exchange_forward(feats, so, sl, ro)
+    grads = [frng.standard_normal(ref[r].shape).astype(np.float32) for r in range(W)]
+    refb = O.exchange_backward(grads, nl, so, sl, ro)
+    for cls in (D.FeatureExchanger, D.IPCExchanger):
+        e = cls(wait_ns=10_000_000_000)
+        xb = cls.allocate_ipc_buffer(max(1, nl[rank] + total_recv), F, dev.index)
+        gb = cls.allocate_ipc_buffer(max(1, total_send), F, dev.index)
+        assert xb.shape == (max(1, nl[rank] + total_recv), F) and xb.is_cuda and float(xb.abs().sum()) == 0.0
+        hx, hg = e.export_ipc_handle(xb), e.export_ipc_handle(gb)
+        assert len(hx) == 64 and all(isinstance(v, int) for v in hx)
+        args = (xb, gb, gather_bytes(hx), gather_bytes(hg), info.send_offsets, info.send_local_indices.to(dev),
+                info.recv_offsets, all_ro, all_nl, nl[rank], F, rank, W)
+        if cls is D.FeatureExchanger:
+            e.setup_ipc(*args)
+        else:
+            e.setup(*args)
+        e.setup_sync(gather_bytes(e.create_and_export_sync_handle()))
+        word, seen = torch.zeros(1, dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev)
+        e.set_watchdog_flags(word, seen)
+        word.fill_(4 if rank == 0 else 0)
+        xt, gt = torch.as_tensor(feats[rank], device=dev), torch.as_tensor(grads[rank], device=dev)
+        for it in range(3):
+            if cls is D.FeatureExchanger:
+                assert e.is_ipc_setup()
+                out = e.feature_push_forward(xt, info)
+                back = e.feature_push_backward(gt, xt.shape, info)
+            else:
+                assert e.is_setup() and not e.use_fabric()
+                xb[:nl[rank]].copy_(xt)
+                e.push_forward(xb)
+                e.record_push_complete()
+                e.wait_for_pushes()
+                out = xb.clone()
+                dist.barrier()          # caller-owned single buffers: nobody may push again before all have read
+                e.push_backward(gt)
+                e.record_push_complete()
+                e.wait_for_pushes()
+                back = gt[:nl[rank]].clone().index_add_(0, info.send_local_indices.to(dev), gb[:total_send])
+                torch.cuda.synchronize()
+                dist.barrier()
+            assert np.array_equal(out[:nl[rank] + total_recv].cpu().numpy(), ref[rank]), f"{cls.__name__} forward"
+            np.testing.assert_allclose(back.cpu().numpy(), refb[rank], rtol=1e-6, atol=1e-6)
+            assert int(seen.item()) == 4
+        e.check_status()
+        dist.barrier()
+        e.teardown()
+        del xb, gb
+
     # DistGraphBuilder across real ranks: the union of the ranks' edges is the full graph, the halo
     # CSR equals the oracle's build_halo_maps for the partition the ranks agreed on
     from dynamis_b200.dist_graph_builder import BuildMode, DistGraphBuilder

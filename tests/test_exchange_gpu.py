@@ -145,19 +145,175 @@ def test_emulated_ranks_match_oracle(cuda, W, F, dtype):
 
 
 def test_wait_budget_expires_with_status_not_a_hang(cuda):
-    """A peer that never signals: the bounded wait runs out after its budget, sets the status word,
-    and the context stays usable."""
+    """A peer that never signals: the bounded wait runs out after its budget, sets the status words,
+    and the context stays usable.  The library path reports it by itself: the next push raises
+    without anybody calling check_status, and the exchanger stays unusable until it is set up again."""
     p0 = (np.array([0, 0, 2]), np.array([0, 1]), np.array([0, 0, 2]), 4)
     p1 = (np.array([0, 2, 2]), np.array([0, 1]), np.array([0, 2, 2]), 4)
     ex = _make_ranks([p0, p1], 4, cuda, wait_ns=2_000_000)  # 2 ms
     x = torch.randn(4, 4, device=cuda)
     out, gen = ex[0].forward_begin(x)       # rank 1 never pushes
     ex[0].forward_end(out, gen)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="timed out"):
+        ex[0].feature_push_forward(x)       # no check_status(): the push itself notices
+    with pytest.raises(RuntimeError, match="set up again"):
+        ex[0].feature_push_backward(torch.zeros(6, 4, device=cuda))
     with pytest.raises(RuntimeError, match="timed out"):
         ex[0].check_status()
     assert torch.equal(x + 0, x)  # the device still works
     for e in ex:
         e.teardown()
+
+
+def test_drift_word_rides_on_every_handshake(cuda):
+    """Every signal carries the rank's drift word; after every wait each rank holds the OR over all
+    ranks (the scheme of the reference's dynamis/tests/test_drift_watchdog.py:97-120), forward and
+    reverse, over 50 generations with random words."""
+    W, F = 4, 8
+    rng = np.random.default_rng(5)
+    n, L = 3000, 36.0
+    pos = (rng.random((n, 3)) * L).astype(np.float32)
+    g = O.radius_graph(pos, (np.eye(3) * L).astype(np.float32), [1, 1, 1], np.float32(6.5))
+    pid = O.sfc_partition(pos, None, W, 0)
+    maps = [O.build_halo_maps(g["src"], g["dst"], pid, r, W) for r in range(W)]
+    plans = [(m["send_offsets"], m["send_local_indices"], m["recv_offsets"], m["num_local"]) for m in maps]
+    ex = _make_ranks(plans, F, cuda)
+    local = [torch.zeros(1, dtype=torch.int32, device=cuda) for _ in range(W)]
+    glob = [torch.full((1,), -1, dtype=torch.int32, device=cuda) for _ in range(W)]
+    for e, l, gl in zip(ex, local, glob):
+        e.set_watchdog_flags(l, gl)
+    feats = [torch.randn(m["num_local"], F, device=cuda) for m in maps]
+    for it in range(50):
+        words = rng.integers(0, 4, W) if it % 5 else np.zeros(W, dtype=np.int64)
+        for l, w in zip(local, words):
+            l.fill_(int(w))
+        out = _exchange_all(ex, feats)
+        want = int(np.bitwise_or.reduce(words))
+        assert [int(x.item()) for x in glob] == [want] * W, f"forward generation {it}"
+        words2 = rng.integers(0, 4, W)
+        for l, w in zip(local, words2):
+            l.fill_(int(w))
+        _exchange_back_all(ex, [torch.ones_like(o) for o in out])
+        assert [int(x.item()) for x in glob] == [int(np.bitwise_or.reduce(words2))] * W, f"reverse generation {it}"
+    ex[1].clear_watchdog_flags()     # a rank that stops carrying the flag contributes 0 and leaves its own word alone
+    glob[1].fill_(77)
+    for l in local:
+        l.fill_(1)
+    local[1].fill_(2)
+    _exchange_all(ex, feats)
+    assert [int(x.item()) for x in glob] == [1, 77, 1, 1]
+    with pytest.raises(RuntimeError, match="int32"):
+        ex[0].set_watchdog_flags(torch.zeros(1, device=cuda), glob[0])
+    for e in ex:
+        e.check_status()
+        e.teardown()
+
+
+def test_results_live_in_peer_visible_slots_and_fall_back_when_held(cuda):
+    """From the second generation on the ghost rows land in the result tensor itself (a slot of the
+    exchange allocation).  A caller that keeps every result alive exhausts the ring; the exchange then
+    goes through the staging buffer and must still be right, and earlier results must stay intact."""
+    W, F = 3, 16
+    rng = np.random.default_rng(11)
+    n, L = 4000, 40.0
+    pos = (rng.random((n, 3)) * L).astype(np.float32)
+    g = O.radius_graph(pos, (np.eye(3) * L).astype(np.float32), [1, 1, 1], np.float32(6.5))
+    pid = O.sfc_partition(pos, None, W, 0)
+    maps = [O.build_halo_maps(g["src"], g["dst"], pid, r, W) for r in range(W)]
+    plans = [(m["send_offsets"], m["send_local_indices"], m["recv_offsets"], m["num_local"]) for m in maps]
+    so, sl, ro = [m["send_offsets"] for m in maps], [m["send_local_indices"] for m in maps], [m["recv_offsets"] for m in maps]
+    ex = _make_ranks(plans, F, cuda)
+
+    def inside(e, t):
+        return e._alloc.ptr <= t.data_ptr() < e._alloc.ptr + e.layout["stage_off"][0]
+
+    held, refs = [], []
+    for it in range(8):
+        feats = [rng.standard_normal((m["num_local"], F)).astype(np.float32) for m in maps]
+        out = _exchange_all(ex, [torch.as_tensor(f, device=cuda) for f in feats])
+        ref = O.exchange_forward(feats, so, sl, ro)
+        for r in range(W):
+            np.testing.assert_array_equal(out[r].cpu().numpy(), ref[r])
+        if it == 0:
+            assert not any(inside(e, o) for e, o in zip(ex, out))     # nothing was announced before the first signal
+        elif it < 4:
+            assert all(inside(e, o) for e, o in zip(ex, out)), it      # ring of 3 slots
+        held.append(out)
+        refs.append(ref)
+        if it >= 4:
+            # ring exhausted by the results still held: staging path, and nothing held was overwritten
+            assert not any(inside(e, o) for e, o in zip(ex, out)), it
+        for o_old, r_old in zip(held, refs):
+            for r in range(W):
+                np.testing.assert_array_equal(o_old[r].cpu().numpy(), r_old[r])
+    del held, out, o_old
+    for it in range(3):  # slots are free again once the tensors are gone
+        feats = [rng.standard_normal((m["num_local"], F)).astype(np.float32) for m in maps]
+        out = _exchange_all(ex, [torch.as_tensor(f, device=cuda) for f in feats])
+        ref = O.exchange_forward(feats, so, sl, ro)
+        for r in range(W):
+            np.testing.assert_array_equal(out[r].cpu().numpy(), ref[r])
+        if it >= 1:
+            assert all(inside(e, o) for e, o in zip(ex, out))
+        del out
+    for e in ex:
+        e.check_status()
+        e.teardown()
+
+
+@pytest.mark.parametrize("ring", [0, 3])
+def test_copy_engine_variant_matches(cuda, ring):
+    """set_ce_threshold_bytes: pack + one peer copy per rank instead of SM stores (reference:
+    ipc_exchanger.cpp:526-569); same rows."""
+    W, F = 3, 32
+    rng = np.random.default_rng(21)
+    n, L = 3000, 36.0
+    pos = (rng.random((n, 3)) * L).astype(np.float32)
+    g = O.radius_graph(pos, (np.eye(3) * L).astype(np.float32), [1, 1, 1], np.float32(6.5))
+    pid = O.sfc_partition(pos, None, W, 0)
+    maps = [O.build_halo_maps(g["src"], g["dst"], pid, r, W) for r in range(W)]
+    plans = [(m["send_offsets"], m["send_local_indices"], m["recv_offsets"], m["num_local"]) for m in maps]
+    so, sl, ro = [m["send_offsets"] for m in maps], [m["send_local_indices"] for m in maps], [m["recv_offsets"] for m in maps]
+    ex = [D.FeatureExchanger(5_000_000_000, result_ring=ring) for _ in range(W)]
+    metas = [ex[r].local_setup(torch.as_tensor(p[0]), torch.as_tensor(p[1]), torch.as_tensor(p[2]), p[3], F, r, W, cuda)
+             for r, p in enumerate(plans)]
+    for e in ex:
+        e.connect(metas)
+        e.set_ce_threshold_bytes(1)
+        assert e.ce_threshold_bytes() == 1
+    for it in range(3):
+        feats = [rng.standard_normal((m["num_local"], F)).astype(np.float32) for m in maps]
+        out = _exchange_all(ex, [torch.as_tensor(f, device=cuda) for f in feats])
+        ref = O.exchange_forward(feats, so, sl, ro)
+        for r in range(W):
+            np.testing.assert_array_equal(out[r].cpu().numpy(), ref[r])
+    for e in ex:
+        e.check_status()
+        e.teardown()
+
+
+def test_push_rows_skips_and_reports_rows_out_of_range(cuda):
+    """dynb_push_rows with a source index outside the input and a destination row beyond the target's
+    capacity: both rows are skipped (nothing is written out of bounds) and the bad word is set."""
+    import ctypes
+
+    from dynamis_b200 import _lib
+
+    L = _lib.lib()
+    x = torch.arange(40, dtype=torch.float32, device=cuda).reshape(10, 4)
+    dst = torch.full((6, 4), -1.0, device=cuda)
+    guard = dst.clone()
+    idx = torch.tensor([0, 3, 99, -1, 5], dtype=torch.int64, device=cuda)   # two bad source rows
+    # one target: capacity 4 rows, rows start at row 0 -> logical row 4 would land on row 4 >= capacity
+    table = torch.tensor([dst.data_ptr(), 0, 0, 5, 4], dtype=torch.int64, device=cuda)
+    bad = torch.zeros(1, dtype=torch.int32, device=cuda)
+    st = torch.cuda.current_stream().cuda_stream
+    assert L.dynb_push_rows(x.data_ptr(), 10, 16, idx.data_ptr(), 0, table.data_ptr(), 1, 5, 16, bad.data_ptr(), st) == 0
+    torch.cuda.synchronize()
+    assert int(bad.item()) == 1
+    assert torch.equal(dst[0], x[0]) and torch.equal(dst[1], x[3])
+    assert torch.equal(dst[2:], guard[2:])
 
 
 def test_backward_before_setup_raises(cuda):

@@ -54,6 +54,34 @@ def test_steps_bit_exact_vs_oracle(cuda, kind, n):
     np.testing.assert_array_equal(tp.cpu().numpy(), pos)
 
 
+@pytest.mark.parametrize("n", [1, 257, 100_003])
+def test_steps_bit_exact_vs_reference_kernels(cuda, ref_ops, n):
+    """The reference's own integrator kernels (compiled from its sources by oracle/build_ref.py) next to
+    ours on the same state: all five steps, every float equal."""
+    dt, gamma, kT = 0.5, 0.01, 0.0257
+    for kind in (I.EULER, I.VERLET1, I.VERLET2, I.LANGEVIN1, I.LANGEVIN2):
+        pos, vel, frc, mass, noise = _state(n, 140 + kind)
+        tp, tv, tf, tm, tn = (_t(a, cuda) for a in (pos, vel, frc, mass, noise))
+        rp, rv = _t(pos, cuda), _t(vel, cuda)
+        if kind == I.EULER:
+            I.Euler.step_(tp, tv, tf, tm, dt)
+            ref_ops.euler_step(rp, rv, tf, tm, dt)
+        elif kind == I.VERLET1:
+            I.Verlet(dt).halfstep1_(tp, tv, tf, tm, dt)
+            ref_ops.verlet_halfstep1(rp, rv, tf, tm, dt)
+        elif kind == I.VERLET2:
+            I.Verlet(dt).halfstep2_(tv, tf, tm, dt)
+            ref_ops.verlet_halfstep2(rv, tf, tm, dt)
+        elif kind == I.LANGEVIN1:
+            I.Langevin(dt, gamma, kT).halfstep1_(tp, tv, tf, tm, tn, dt)
+            ref_ops.langevin_halfstep1(rp, rv, tf, tm, tn, gamma, kT, dt)
+        else:
+            I.Langevin(dt, gamma, kT).halfstep2_(tv, tf, tm, tn, dt)
+            ref_ops.langevin_halfstep2(rv, tf, tm, tn, gamma, kT, dt)
+        assert torch.equal(tv, rv), f"velocities differ from the reference kernel (kind {kind})"
+        assert torch.equal(tp, rp), f"positions differ from the reference kernel (kind {kind})"
+
+
 def test_analytic_cases(cuda):
     mk = lambda rows: torch.tensor(rows, dtype=torch.float32, device=cuda)
     # zero force: velocity unchanged, position advances by v dt

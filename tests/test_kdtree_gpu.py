@@ -44,8 +44,8 @@ def test_labels_match_oracle(cuda, W, weighted):
 
 
 @pytest.mark.parametrize("W", [2, 7, 8, 64, 300])
-def test_selection_and_sorted_paths_agree(cuda, W, monkeypatch):
-    """Equal-count cuts come from a selection (no sort); DYNB_KD_SORT forces the sorted path, which the
+def test_selection_and_sorted_paths_agree(cuda, W):
+    """Equal-count cuts come from a selection (no sort); sorted_cuts takes the sorted path, which the
     weighted cuts always use.  Same labels on inputs with many repeated coordinates."""
     rng = np.random.default_rng(41 + W)
     pos = (rng.random((20_000, 3)) * 8.0).astype(np.float32)
@@ -53,8 +53,7 @@ def test_selection_and_sorted_paths_agree(cuda, W, monkeypatch):
     pos[3000:3500] = pos[3000]
     tp = torch.as_tensor(pos, device=cuda)
     by_selection = D.kdtree_partition_labels(tp, None, W)
-    monkeypatch.setenv("DYNB_KD_SORT", "1")
-    by_sort = D.kdtree_partition_labels(tp, None, W)
+    by_sort = D.kdtree_partition_labels(tp, None, W, sorted_cuts=True)
     assert torch.equal(by_selection, by_sort)
     np.testing.assert_array_equal(by_selection.cpu().numpy(), O.kdtree_partition(pos, None, W))
 

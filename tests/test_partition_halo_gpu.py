@@ -259,6 +259,29 @@ def test_sfc_vs_reference_kernels(cuda, ref_ops, curve):
             assert torch.equal(D.sfc_partition_labels(pos, w, W, curve), ref_ops.sfc_partition(pos, w, W, curve))
 
 
+def test_hilbert_labels_equal_reference_when_keys_are_distinct(cuda, ref_ops):
+    """The reference's 7-bit "Hilbert" keys tie massively on ordinary inputs and its sort leaves ties
+    unspecified; on an input whose keys are all distinct its labels are defined, and ours must equal
+    them exactly (equal counts and weighted)."""
+    rng = np.random.default_rng(77)
+    grid = rng.integers(0, 128, (60_000, 3))
+    grid[0], grid[1] = 0, 127                       # pin the bounding box
+    pos = grid.astype(np.float32)
+    keys = O.sfc_keys(pos, 1)
+    _, first = np.unique(keys, return_index=True)
+    keep = np.union1d(first, [0, 1])
+    keep = keep[np.argsort(rng.random(keep.size))]  # atom order unrelated to key order
+    pos = pos[keep]
+    assert np.unique(O.sfc_keys(pos, 1)).size == pos.shape[0]   # same bounding box, so the keys did not change
+    n = pos.shape[0]
+    assert n > 500
+    tp = torch.as_tensor(pos, device=cuda)
+    w = torch.as_tensor(rng.integers(1, 300, n), device=cuda)
+    for W in (2, 8, 13):
+        assert torch.equal(D.sfc_partition_labels(tp, None, W, 1), ref_ops.sfc_partition(tp, None, W, 1))
+        assert torch.equal(D.sfc_partition_labels(tp, w, W, 1), ref_ops.sfc_partition(tp, w, W, 1))
+
+
 def test_halo_ops_vs_reference_kernels(cuda, ref_ops):
     pos, cell = _halo_case(13)
     n, W = pos.shape[0], 4

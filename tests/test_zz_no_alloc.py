@@ -56,6 +56,24 @@ def test_static_scratch_partition_matches_workspace_partition(cuda):
         assert torch.equal(a, b) and torch.equal(pa, pb)
         a, pa, b, pb = _both(L, pos2, w2, 5, 0, cuda)
         assert torch.equal(a, b) and torch.equal(pa, pb)
+        # without the permutation output (dynb_sfc_partition then selects the split points without a sort when
+        # it has its full workspace; the built-in scratch always sorts): same labels
+        st = torch.cuda.current_stream(cuda).cuda_stream
+        c = torch.full((30_001,), -3, dtype=torch.int64, device=cuda)
+        _lib.check(L.dynb_sfc_partition_static(pos2.data_ptr(), 30_001, w2.data_ptr(), 5, 0, c.data_ptr(), None, st),
+                   "sfc_partition_static")
+        torch.cuda.synchronize(cuda)
+        assert torch.equal(c, b)
+        # "allocates nothing": the free device memory is the same before and after two more calls
+        big = torch.empty(max_atoms, dtype=torch.int64, device=cuda)
+        torch.cuda.synchronize(cuda)
+        free0, _ = torch.cuda.mem_get_info(cuda)
+        for _ in range(2):
+            _lib.check(L.dynb_sfc_partition_static(pos1.data_ptr(), max_atoms, None, 8, 0, big.data_ptr(), None, st),
+                       "sfc_partition_static")
+        torch.cuda.synchronize(cuda)
+        free1, _ = torch.cuda.mem_get_info(cuda)
+        assert free1 == free0, (free0, free1)
         # larger than the limit: refused with a clear message, nothing launched
         pos3 = torch.zeros(max_atoms + 1, 3, device=cuda)
         out = torch.empty(max_atoms + 1, dtype=torch.int64, device=cuda)
