@@ -2,16 +2,20 @@
 """Benchmark of the hot path: periodic radius graph (+ Morton partition, + halo exchange when N > 1).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload fcc|liquid] [--exchange peer|nccl] [--ce-threshold BYTES]      (N > 1 only)
 
 N > 1 is launched by torchrun (one rank per GPU, NCCL).  Prints ONE JSON line on rank 0.
 
 A "step" is one pass of the path over one batch of synthetic input:
   N = 1   the 1,000,000-atom random liquid (density 0.1 atoms/Å^3, L = 215.4 Å, fp32, r = 5 Å):
           Morton-key partition + radius graph (edge_index, shifts, degrees).
-  N > 1   the same liquid with N x 1,000,000 atoms, cut into N subdomains along the Morton curve;
-          every rank exchanges halo positions, builds the graph of its own atoms over
-          [owned | halo], then exchanges two layers of 128-wide node embeddings forward and the
-          force gradients backward (weak scaling: per-GPU work is fixed).
+  N > 1   the 8,001,504-atom fcc Cu supercell (fp32, r = 6 Å, halo 12 Å) cut into N subdomains along
+          the Morton curve (strong scaling); every rank exchanges halo positions, builds the graph
+          of its own atoms over [owned | halo], then exchanges two layers of 128-wide node
+          embeddings forward and the three gradients backward.  Before anything is timed one whole
+          step is checked on every rank (ghost rows, reverse sums, union of the edge sets) and the
+          run exits non-zero on a mismatch.  --workload liquid: N x 1,000,000 atoms of the liquid
+          (weak scaling).
 
 value       whole-job edges/s with inputs resident in HBM, CUDA-event time, max over ranks.
 e2e         the same through the public API with the positions arriving from pinned host memory
@@ -20,7 +24,11 @@ roofline    the dominant kernel (the edge-writing pass of the cell scan) timed a
             measured HBM copy bandwidth of MEASURED_PEAKS.json.
 cpu_baseline / --impl reference
             the CPU restatement of the reference's algorithm (oracle/, OpenMP over all host
-            threads) on the same workload; the reference itself has no CPU radius-graph path.
+            threads) on the same workload (at N > 1: rank 0's share of it); the reference itself
+            has no CPU radius-graph path.
+reference_cuda (N = 1)
+            the reference's own CUDA kernels, compiled for sm_100 by oracle/build_ref.py, timed on
+            the same inputs and GPU outside every timed region of this implementation.
 """
 
 from __future__ import annotations
@@ -115,17 +123,26 @@ def liquid(n_atoms: int):
     return synthetic.random_liquid(n_atoms, density=DENSITY, seed=SEED, radius=RADIUS)
 
 
+def host_threads() -> int:
+    """Threads the CPU arm uses: every core this process may run on (launchers such as torchrun export
+    OMP_NUM_THREADS=1, so the count is passed to the oracle explicitly)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_baseline(sample_atoms: int, steps: int = 1):
     """Oracle (CPU port of the reference algorithm) on a liquid of `sample_atoms` atoms, all host threads."""
     from oracle import cpu_oracle as O
 
     pos, cell, pbc, r = liquid(sample_atoms)
-    threads = O.max_threads()
+    threads = host_threads()
     best = None
     E = 0
     for _ in range(max(1, steps)):
         t = time.perf_counter()
-        g = O.radius_graph(pos, cell, pbc, r)
+        g = O.radius_graph(pos, cell, pbc, r, nthreads=threads)
         dt = time.perf_counter() - t
         E = g["E"]
         best = dt if best is None else min(best, dt)
@@ -133,36 +150,109 @@ def cpu_baseline(sample_atoms: int, steps: int = 1):
             "sample": f"{sample_atoms} atoms of the same liquid (density {DENSITY}, r = {RADIUS}), {E} edges, best of {max(1, steps)}"}, best
 
 
+def reference_workload(n_gpus: int, workload: str):
+    """What the CPU arm computes: at N = 1 the whole single-GPU workload; at N > 1 rank 0's share of the
+    N-GPU workload — the graph of the atoms rank 0 owns over [owned | atoms within the halo width of its
+    bounding box] (a superset of its halo, so the edges are those of the whole-system graph)."""
+    from oracle import cpu_oracle as O
+
+    if n_gpus <= 1:
+        pos, cell, pbc, r = liquid(ATOMS_PER_GPU)
+        return pos, cell, pbc, r, None, ("random liquid 1,000,000 atoms, density 0.1 atoms/A^3, cubic periodic box L=215.4 A, fp32, "
+                                         "cutoff 5.0 A (configs[1]): radius graph of all atoms")
+    if workload == "liquid":
+        pos, cell, pbc, r = liquid(ATOMS_PER_GPU * n_gpus)
+        halo, name = r + 0.5, f"random liquid {ATOMS_PER_GPU * n_gpus} atoms, cutoff 5.0 A"
+    else:
+        from dynamis_b200 import synthetic
+
+        pos, cell, pbc, r = synthetic.fcc_copper(126, seed=1004)
+        halo, name = r + 6.0, f"fcc Cu {pos.shape[0]} atoms, cutoff 6.0 A (configs[3])"
+    labels = O.sfc_partition(pos, None, n_gpus, 0)
+    own = np.nonzero(labels == 0)[0]
+    L = np.diag(cell).astype(np.float64)
+    p64 = pos.astype(np.float64)
+    w = p64  # not wrapped: a subdomain is compact in the coordinates the curve was built on
+    lo, hi = w[own].min(axis=0), w[own].max(axis=0)
+    keep = np.ones(pos.shape[0], dtype=bool)
+    for k in range(3):
+        centre, half = (lo[k] + hi[k]) / 2, (hi[k] - lo[k]) / 2
+        d = np.abs(((w[:, k] - centre + L[k] / 2) % L[k]) - L[k] / 2) - half
+        keep &= d <= halo
+    keep[own] = True
+    idx = np.nonzero(keep)[0]
+    sub = pos[idx]
+    targets = np.searchsorted(idx, own).astype(np.int64)
+    return sub, cell, pbc, r, targets, (f"{name}, Morton partition into {n_gpus}: rank 0's share, graph of its {own.size} owned atoms "
+                                        f"over {idx.size} positions (owned + everything within {halo} A of their bounding box)")
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = 250_000
-    base, _ = cpu_baseline(sample, steps=1)  # warm-up (page in, build)
     from oracle import cpu_oracle as O
 
-    pos, cell, pbc, r = liquid(sample)
-    for _ in range(min(args.warmup, 2)):
-        O.radius_graph(pos, cell, pbc, r)
-    t0 = time.perf_counter()
+    threads = host_threads()
+    pos, cell, pbc, r, targets, what = reference_workload(args.gpus, args.workload)
     E = 0
+    for _ in range(min(args.warmup, 1)):  # page in, build
+        E = O.radius_graph(pos, cell, pbc, r, targets=targets, nthreads=threads)["E"]
+    t0 = time.perf_counter()
     for _ in range(args.steps):
-        E = O.radius_graph(pos, cell, pbc, r)["E"]
+        E = O.radius_graph(pos, cell, pbc, r, targets=targets, nthreads=threads)["E"]
     dt = time.perf_counter() - t0
     v = E * args.steps / dt
     line = {
         "impl": "reference", "metric": "radius_graph_edges_per_s", "value": v, "unit": "edges/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "random liquid 1,000,000 atoms/GPU, density 0.1, r=5.0, fp32 (configs[1]); "
-                               f"CPU arm timed on a {sample}-atom sample of it"},
-        "cpu_baseline": {"value": v, "unit": "edges/s", "cores": base["cores"], "kind": "port",
-                         "sample": f"{sample}-atom liquid, {E} edges per step"},
+        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak" if (args.gpus <= 1 or args.workload == "liquid") else "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": what, "edges_per_step": E},
+        "cpu_baseline": {"value": v, "unit": "edges/s", "cores": threads, "kind": "port",
+                         "sample": f"{E} edges per step, {args.steps} steps"},
         "e2e": {"value": v, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-        "note": "the reference has no CPU radius-graph path; this is the CPU port of its algorithm (oracle/)",
+        "note": "the reference has no CPU radius-graph path (radius_graph.cpp requires CUDA tensors); this is the CPU restatement of "
+                "its algorithm (oracle/), OpenMP over all host threads; a CPU's edges/s does not depend on how many GPUs the "
+                "other arm uses, so at N > 1 one rank's share of the job is timed",
     }
     print(json.dumps(line), flush=True)
+
+
+def reference_cuda(pos, cell, pbc, r, E):
+    """The reference's own CUDA kernels (compiled for sm_100 from its sources by oracle/build_ref.py) on the
+    same inputs and the same GPU, outside every timed region of this implementation: the bar this
+    implementation is measured against.  None when that library was not built."""
+    import torch
+
+    from oracle import build_ref
+
+    if not build_ref.load():
+        return None
+    ops = torch.ops.dynamis_ref
+    cell_d, pbc_d = cell.to(pos.device), pbc.to(pos.device)
+
+    def med(fn, warm=5, reps=20):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return float(np.median(ts))
+
+    g = med(lambda: ops.radius_graph(pos, cell_d, pbc_d, r, None, False))
+    s = med(lambda: ops.sfc_partition(pos, None, 8, 0))
+    k = med(lambda: ops.kdtree_partition(pos, None, 8))
+    return {"graph_ms": g, "sfc_ms": s, "kdtree_ms": k, "edges_per_s": E / ((g + s) * 1e-3),
+            "what": "reference CUDA kernels (radius_graph_pbc_cuda_impl_ex, sfc_partition_cuda_impl, kdtree_bisect_cuda_impl) "
+                    "compiled for sm_100, CUDA events, median of 20 after 5 warm-up calls; edges_per_s over graph + Morton partition"}
 
 
 def run_ours(args):
@@ -255,7 +345,9 @@ def run_ours(args):
     e2e_s = (time.perf_counter() - t0) / K
     assert int(nni_pin.item()) == E
     e2e = {"value": E / e2e_s, "unit": "edges/s", "ms_per_step": e2e_s * 1e3,
-           "h2d_bytes_per_step": int(pos_pin.numel() * 4), "d2h_bytes_per_step": int(N * 4 + 8)}
+           "h2d_bytes_per_step": int(pos_pin.numel() * 4), "d2h_bytes_per_step": int(N * 4 + 8),
+           "note": "positions in from pinned host memory, degrees and edge count out; the 1.47 GB edge list stays on the device, "
+                   "as with the API it replaces (CUDA tensors for a CUDA consumer)"}
 
     # ---- the dominant kernel alone (edge-writing pass), CUDA events on its stream, L2 flushed
     plan = G.plan_radius_graph(pos, cell, pbc, r)
@@ -290,6 +382,7 @@ def run_ours(args):
     del ei, sh
 
     base, _ = cpu_baseline(ATOMS_PER_GPU, steps=1)
+    ref_cuda = reference_cuda(pos, cell, pbc, r, E)
 
     line = {
         "metric": "radius_graph_edges_per_s", "value": value, "unit": "edges/s", "n_gpus": 1, "steps": K, "warmup": W,
@@ -298,7 +391,7 @@ def run_ours(args):
         "config": {"workload": "random liquid 1,000,000 atoms, density 0.1 atoms/A^3, cubic periodic box L=215.4 A, fp32, "
                                "cutoff 5.0 A (configs[1]): " + ("Morton partition + " if have_sfc else "") + "radius graph",
                    "edges_per_step": E, "l2": "256 MiB buffer written between timed steps; a step itself writes 1.5 GB"},
-        "roofline": roofline, "cpu_baseline": base, "e2e": e2e, "clocks": clocks,
+        "roofline": roofline, "cpu_baseline": base, "reference_cuda": ref_cuda, "e2e": e2e, "clocks": clocks,
         "gpu_launches": D.launches_per_graph() + (D.launches_per_partition() if have_sfc else 0),
         "halo_exchange_ms_per_step": None,
         # the radius graph alone (the step also holds the Morton partition), for comparison with the N > 1 lines
@@ -313,6 +406,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="fcc", choices=["fcc", "liquid"],
+                    help="N > 1 only: fcc = 8,001,504-atom fcc Cu cut into N subdomains (strong scaling), liquid = N x 1,000,000 atoms")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="N > 1 only: one-sided peer stores or NCCL all-to-all")
+    ap.add_argument("--ce-threshold", type=int, default=0, help="N > 1, peer exchange: copy-engine threshold in bytes (0 = SM stores)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

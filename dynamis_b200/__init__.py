@@ -47,3 +47,17 @@ from .state import (  # noqa: F401
 )
 
 from . import integrators  # noqa: F401,E402
+from .dist_env import TorchDistEnv  # noqa: F401,E402
+
+
+def install_shim() -> str:
+    """Puts dynamis_b200/shim first on sys.path, so that ``import dynamis_state`` / ``import dynamis_model``
+    resolve to this implementation for the reference's unchanged callers.  Returns the directory."""
+    import os
+    import sys
+
+    d = os.path.join(os.path.dirname(os.path.abspath(__file__)), "shim")
+    if d in sys.path:
+        sys.path.remove(d)
+    sys.path.insert(0, d)
+    return d

@@ -191,33 +191,61 @@ __device__ void last_block_signals(const dynb_halo_ctx& c, int dir, uint32_t gen
 }
 
 // byte range [0, bytes) copied by `parts` blocks, this block being `part`; vb = 16, 4 or 1 is the
-// widest unit both pointers are aligned to.
+// widest unit both pointers are aligned to.  Blocks interleave (block-sized pieces, grid stride): all
+// resident blocks then stream through neighbouring addresses, which HBM serves about a quarter faster
+// than one far-apart chunk per block.
 __device__ void copy_span(unsigned char* __restrict__ dst, const unsigned char* __restrict__ src, int64_t bytes, int vb,
                           int64_t part, int64_t parts)
 {
     if (vb == 16) {
+        constexpr int U = 8;
         const int64_t n = bytes >> 4;
-        const int64_t lo = n * part / parts, hi = n * (part + 1) / parts;
         const uint4* s = reinterpret_cast<const uint4*>(src);
         uint4* d = reinterpret_cast<uint4*>(dst);
-        int64_t i = lo + threadIdx.x;
-        for (; i + 3 * (int64_t)blockDim.x < hi; i += 4 * (int64_t)blockDim.x) {
-            const uint4 a = __ldcs(s + i), b = __ldcs(s + i + blockDim.x), e = __ldcs(s + i + 2 * blockDim.x),
-                        f = __ldcs(s + i + 3 * blockDim.x);
-            d[i] = a; d[i + blockDim.x] = b; d[i + 2 * blockDim.x] = e; d[i + 3 * blockDim.x] = f;
+        const int64_t bd = blockDim.x, step = parts * bd * U;
+        int64_t i = part * bd * U + threadIdx.x;
+        for (; i + (U - 1) * bd < n; i += step) {
+            uint4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) v[u] = __ldcs(s + i + u * bd);
+#pragma unroll
+            for (int u = 0; u < U; u++) d[i + u * bd] = v[u];
         }
-        for (; i < hi; i += blockDim.x) d[i] = __ldcs(s + i);
-        if (part == 0) for (int64_t t = (n << 4) + threadIdx.x; t < bytes; t += blockDim.x) dst[t] = src[t];
+        for (int u = 0; u < U; u++)
+            if (i + u * bd < n) d[i + u * bd] = __ldcs(s + i + u * bd);
+        if (part == 0) for (int64_t t = (n << 4) + threadIdx.x; t < bytes; t += bd) dst[t] = src[t];
     } else if (vb == 4) {
         const int64_t n = bytes >> 2;
-        const int64_t lo = n * part / parts, hi = n * (part + 1) / parts;
         const uint32_t* s = reinterpret_cast<const uint32_t*>(src);
         uint32_t* d = reinterpret_cast<uint32_t*>(dst);
-        for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) d[i] = s[i];
+        for (int64_t i = part * blockDim.x + threadIdx.x; i < n; i += parts * blockDim.x) d[i] = s[i];
         if (part == 0) for (int64_t t = (n << 2) + threadIdx.x; t < bytes; t += blockDim.x) dst[t] = src[t];
     } else {
-        const int64_t lo = bytes * part / parts, hi = bytes * (part + 1) / parts;
-        for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) dst[i] = src[i];
+        for (int64_t i = part * blockDim.x + threadIdx.x; i < bytes; i += parts * blockDim.x) dst[i] = src[i];
+    }
+}
+
+// Rows of q 16-byte units whose flag is zero, copied one warp per row, R rows in flight per warp.
+__device__ void copy_rows_unflagged(uint4* __restrict__ dst, const uint4* __restrict__ src, const uint8_t* __restrict__ flag,
+                                    int64_t rows, int64_t q, int64_t part, int64_t parts)
+{
+    constexpr int R = 4;
+    const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+    const int64_t nw = parts * wpb, w = part * wpb + (threadIdx.x >> 5);
+    const int64_t lo = rows * w / nw, hi = rows * (w + 1) / nw;
+    for (int64_t r0 = lo; r0 < hi; r0 += R) {
+        bool ok[R];
+#pragma unroll
+        for (int k = 0; k < R; k++) ok[k] = (r0 + k < hi) && flag[r0 + k] == 0;
+        for (int64_t c = lane; c < q; c += 32) {
+            uint4 v[R];
+#pragma unroll
+            for (int k = 0; k < R; k++)
+                if (ok[k]) v[k] = __ldcs(src + (r0 + k) * q + c);
+#pragma unroll
+            for (int k = 0; k < R; k++)
+                if (ok[k]) dst[(r0 + k) * q + c] = v[k];
+        }
     }
 }
 
@@ -233,25 +261,27 @@ __device__ __forceinline__ int find_seg(const PeerSeg* seg, int n, int64_t row)
     return t;
 }
 
-// Rows [lo, hi) (in units of V) of the logical push list stored into the peers.  INDEXED: logical row i
-// is x[index[i]] (forward), else x[src_row_base + i] (ghost-gradient rows).
+// Units [0, total) (V-wide pieces of the logical push list's rows) stored into the peers by `parts` blocks,
+// this block being `part`, interleaved like copy_span.  INDEXED: logical row i is x[index[i]] (forward),
+// else x[src_row_base + i] (ghost-gradient rows).
 template <typename V, bool INDEXED>
 __device__ void push_units(const dynb_halo_ctx& c, const V* __restrict__ x, int64_t n_rows_in, int64_t q,
                            const int64_t* __restrict__ index, int64_t src_row_base, const PeerSeg* seg, int nseg,
-                           int64_t lo, int64_t hi)
+                           int64_t total, int64_t part, int64_t parts)
 {
     constexpr int U = 4;
-    const int64_t step = (int64_t)blockDim.x;
-    for (int64_t base = lo + threadIdx.x; base < hi; base += U * step) {
+    const int64_t bd = blockDim.x, step = parts * bd * U;
+    const bool small = total < (1ll << 32);
+    for (int64_t base = part * bd * U + threadIdx.x; base < total; base += step) {
         V v[U];
         V* d[U];
 #pragma unroll
         for (int u = 0; u < U; u++) {
-            const int64_t i = base + u * step;
+            const int64_t i = base + u * bd;
             d[u] = nullptr;
-            if (i >= hi) continue;
+            if (i >= total) continue;
             int64_t row, col;
-            if (hi < (1ll << 32)) { const uint32_t r32 = (uint32_t)i / (uint32_t)q; row = r32; col = (uint32_t)i - r32 * (uint32_t)q; }
+            if (small) { const uint32_t r32 = (uint32_t)i / (uint32_t)q; row = r32; col = (uint32_t)i - r32 * (uint32_t)q; }
             else { row = i / q; col = i - row * q; }
             const int t = find_seg(seg, nseg, row);
             if (t == nseg) continue;
@@ -271,7 +301,7 @@ __device__ void push_units(const dynb_halo_ctx& c, const V* __restrict__ x, int6
 // result, then the signal.  Even blocks push first and copy second, odd blocks the other way round, so
 // that NVLink stores and the HBM copy run side by side.
 template <typename V>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 halo_forward_begin_kernel(dynb_halo_ctx c, const V* __restrict__ x, int64_t n_local, int64_t q, int64_t row_bytes,
                           const int64_t* __restrict__ send_local, int64_t total_send, unsigned char* __restrict__ out_head,
                           int head_vb, uint32_t gen, uint32_t announce, int skip_push)
@@ -293,13 +323,12 @@ halo_forward_begin_kernel(dynb_halo_ctx c, const V* __restrict__ x, int64_t n_lo
     __syncthreads();
     const int64_t G = gridDim.x, b = blockIdx.x;
     const int64_t P = skip_push ? 0 : total_send * q;
-    const int64_t plo = P * b / G, phi = P * (b + 1) / G;
     const unsigned char* xs = reinterpret_cast<const unsigned char*>(x);
     if (b & 1) {
         if (out_head != nullptr) copy_span(out_head, xs, n_local * row_bytes, head_vb, b, G);
-        push_units<V, true>(c, x, n_local, q, send_local, 0, seg, c.world_size, plo, phi);
+        push_units<V, true>(c, x, n_local, q, send_local, 0, seg, c.world_size, P, b, G);
     } else {
-        push_units<V, true>(c, x, n_local, q, send_local, 0, seg, c.world_size, plo, phi);
+        push_units<V, true>(c, x, n_local, q, send_local, 0, seg, c.world_size, P, b, G);
         if (out_head != nullptr) copy_span(out_head, xs, n_local * row_bytes, head_vb, b, G);
     }
     last_block_signals(c, 0, gen, announce);
@@ -320,7 +349,7 @@ halo_forward_end_kernel(dynb_halo_ctx c, uint32_t gen, unsigned long long budget
 // Reverse halo, first half: the gradient rows of the ghost atoms -> their owners' receive buffers; the
 // gradient rows of owned atoms that receive nothing -> result (has_recv == nullptr: all owned rows); signal.
 template <typename V>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 halo_backward_begin_kernel(dynb_halo_ctx c, const V* __restrict__ g, int64_t n_local, int64_t n_ghost, int64_t q,
                            int64_t row_bytes, const uint8_t* __restrict__ has_recv, unsigned char* __restrict__ out, int out_vb,
                            uint32_t gen)
@@ -339,22 +368,16 @@ halo_backward_begin_kernel(dynb_halo_ctx c, const V* __restrict__ g, int64_t n_l
     __syncthreads();
     const int64_t G = gridDim.x, b = blockIdx.x;
     const int64_t P = n_ghost * q;
-    const int64_t plo = P * b / G, phi = P * (b + 1) / G;
-    for (int pass = 0; pass < 2; pass++) {
-        if ((pass == 0) == ((b & 1) == 0)) {
-            push_units<V, false>(c, g, n_local + n_ghost, q, nullptr, n_local, seg, c.world_size, plo, phi);
-        } else if (has_recv == nullptr) {
-            copy_span(out, reinterpret_cast<const unsigned char*>(g), n_local * row_bytes, out_vb, b, G);
-        } else {
-            // V-wide units of the owned rows, skipping rows that the second half rewrites anyway
-            const int64_t C = n_local * q;
-            const int64_t clo = C * b / G, chi = C * (b + 1) / G;
-            V* o = reinterpret_cast<V*>(out);
-            for (int64_t i = clo + threadIdx.x; i < chi; i += blockDim.x) {
-                const int64_t row = i / q;
-                if (!has_recv[row]) o[i] = g[i];
-            }
-        }
+    const unsigned char* gs = reinterpret_cast<const unsigned char*>(g);
+    // has_recv comes only with V = uint4 (16-byte aligned rows): rows that the second half rewrites anyway are left out
+    if (b & 1) {
+        if (has_recv == nullptr) copy_span(out, gs, n_local * row_bytes, out_vb, b, G);
+        else copy_rows_unflagged(reinterpret_cast<uint4*>(out), reinterpret_cast<const uint4*>(g), has_recv, n_local, q, b, G);
+        push_units<V, false>(c, g, n_local + n_ghost, q, nullptr, n_local, seg, c.world_size, P, b, G);
+    } else {
+        push_units<V, false>(c, g, n_local + n_ghost, q, nullptr, n_local, seg, c.world_size, P, b, G);
+        if (has_recv == nullptr) copy_span(out, gs, n_local * row_bytes, out_vb, b, G);
+        else copy_rows_unflagged(reinterpret_cast<uint4*>(out), reinterpret_cast<const uint4*>(g), has_recv, n_local, q, b, G);
     }
     last_block_signals(c, 1, gen, 0u);
 }
@@ -369,20 +392,47 @@ halo_backward_end_kernel(dynb_halo_ctx c, uint32_t gen, unsigned long long budge
 {
     wait_all(c, 1, gen, budget_ns);
     if (blockIdx.x == 0) drift_or(c, 1, gen);
-    const int64_t total = n_rows * q;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = i / q, col = i - r * q;
-        const int64_t row = rows[r];
-        V v = g[row * q + col];
-        const int64_t b = inv_offsets[row], e = inv_offsets[row + 1];
-        T* a = reinterpret_cast<T*>(&v);
-        for (int64_t k = b; k < e; k++) {
-            const V xx = recv[(int64_t)inv_entries[k] * q + col];
-            const T* xr = reinterpret_cast<const T*>(&xx);
+    // one warp per listed row, R rows in flight; lanes walk the row's V-wide columns
+    constexpr int R = 4;
+    const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+    const int64_t nw = (int64_t)gridDim.x * wpb, w = (int64_t)blockIdx.x * wpb + (threadIdx.x >> 5);
+    for (int64_t r0 = w * R; r0 < n_rows; r0 += nw * R) {
+        int64_t row[R], b[R], e[R];
 #pragma unroll
-            for (int cc = 0; cc < VW; cc++) a[cc] += xr[cc];
+        for (int k = 0; k < R; k++) {
+            row[k] = -1;
+            if (r0 + k < n_rows) { row[k] = rows[r0 + k]; b[k] = inv_offsets[row[k]]; e[k] = inv_offsets[row[k] + 1]; }
         }
-        out[row * q + col] = v;
+        for (int64_t col = lane; col < q; col += 32) {
+            V v[R], f[R];
+            bool hf[R];
+#pragma unroll
+            for (int k = 0; k < R; k++) {
+                hf[k] = false;
+                if (row[k] >= 0) {
+                    v[k] = g[row[k] * q + col];
+                    hf[k] = b[k] < e[k];
+                    if (hf[k]) f[k] = recv[(int64_t)inv_entries[b[k]] * q + col];
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < R; k++) {
+                if (row[k] < 0) continue;
+                T* a = reinterpret_cast<T*>(&v[k]);
+                if (hf[k]) {
+                    const T* fr = reinterpret_cast<const T*>(&f[k]);
+#pragma unroll
+                    for (int cc = 0; cc < VW; cc++) a[cc] += fr[cc];
+                }
+                for (int64_t j = b[k] + 1; j < e[k]; j++) {
+                    const V xx = recv[(int64_t)inv_entries[j] * q + col];
+                    const T* xr = reinterpret_cast<const T*>(&xx);
+#pragma unroll
+                    for (int cc = 0; cc < VW; cc++) a[cc] += xr[cc];
+                }
+                out[row[k] * q + col] = v[k];
+            }
+        }
     }
 }
 
@@ -510,7 +560,7 @@ static inline int span_vb(const void* a, const void* b, int64_t)
 static inline unsigned fused_grid(int64_t units16)
 {
     const int64_t blocks = (units16 + 256 * 8 - 1) / (256 * 8);
-    return (unsigned)std::max<int64_t>(1, std::min<int64_t>(blocks, (int64_t)sm_count_cached() * 8));
+    return (unsigned)std::max<int64_t>(1, std::min<int64_t>(blocks, (int64_t)sm_count_cached() * 6));  // two waves of 3 CTAs per SM
 }
 
 extern "C" int dynb_halo_forward_begin(const dynb_halo_ctx* ctx, const void* x_dev, int64_t n_local, int64_t row_bytes,
@@ -587,22 +637,22 @@ extern "C" int dynb_halo_backward_end(const dynb_halo_ctx* ctx, uint32_t gen, in
     if (dtype == DYNB_F32) {
         if (al && row_bytes % 16 == 0) {
             const int64_t q = row_bytes / 16;
-            halo_backward_end_kernel<float, float4, 4><<<grid_for(n_rows * q), 256, 0, s>>>(
+            halo_backward_end_kernel<float, float4, 4><<<grid_for(n_rows * 32), 256, 0, s>>>(
                 *ctx, gen, bud, static_cast<const float4*>(grad_dev), rows_dev, n_rows, q, static_cast<const float4*>(recv_dev),
                 inv_offsets_dev, inv_entries_dev, static_cast<float4*>(out_dev));
         } else {
-            halo_backward_end_kernel<float, float, 1><<<grid_for(n_rows * feature_dim), 256, 0, s>>>(
+            halo_backward_end_kernel<float, float, 1><<<grid_for(n_rows * 32), 256, 0, s>>>(
                 *ctx, gen, bud, static_cast<const float*>(grad_dev), rows_dev, n_rows, feature_dim, static_cast<const float*>(recv_dev),
                 inv_offsets_dev, inv_entries_dev, static_cast<float*>(out_dev));
         }
     } else {
         if (al && row_bytes % 16 == 0) {
             const int64_t q = row_bytes / 16;
-            halo_backward_end_kernel<double, double2, 2><<<grid_for(n_rows * q), 256, 0, s>>>(
+            halo_backward_end_kernel<double, double2, 2><<<grid_for(n_rows * 32), 256, 0, s>>>(
                 *ctx, gen, bud, static_cast<const double2*>(grad_dev), rows_dev, n_rows, q, static_cast<const double2*>(recv_dev),
                 inv_offsets_dev, inv_entries_dev, static_cast<double2*>(out_dev));
         } else {
-            halo_backward_end_kernel<double, double, 1><<<grid_for(n_rows * feature_dim), 256, 0, s>>>(
+            halo_backward_end_kernel<double, double, 1><<<grid_for(n_rows * 32), 256, 0, s>>>(
                 *ctx, gen, bud, static_cast<const double*>(grad_dev), rows_dev, n_rows, feature_dim, static_cast<const double*>(recv_dev),
                 inv_offsets_dev, inv_entries_dev, static_cast<double*>(out_dev));
         }
