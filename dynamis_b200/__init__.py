@@ -48,6 +48,7 @@ from .state import (  # noqa: F401
 
 from . import integrators  # noqa: F401,E402
 from .dist_env import TorchDistEnv  # noqa: F401,E402
+from .migrate import DistributedSimState  # noqa: F401,E402
 
 
 def install_shim() -> str:

@@ -87,6 +87,9 @@ SIGNATURES = {
     "dynb_sfc_workspace_bytes": (_i32, [_i64, ctypes.POINTER(_i64)]),
     "dynb_sfc_partition": (_i32, [_p, _i64, _p, _i64, _i32, _p, _p, _p, _i64, _p]),
     "dynb_sfc_keys": (_i32, [_p, _i64, _i32, _p, _p, _i64, _p]),
+    "dynb_sfc_minmax": (_i32, [_p, _i64, _p, _p]),
+    "dynb_sfc_keys_from_bounds": (_i32, [_p, _i64, _i32, _p, _p, _p]),
+    "dynb_label_by_splits": (_i32, [_p, _p, _i64, _p, _p, _i32, _p, _p]),
     "dynb_radix_sort_workspace_bytes": (_i32, [_i64, ctypes.POINTER(_i64)]),
     "dynb_radix_sort_pairs": (_i32, [_p, _p, _i64, _i32, _i32, _p, _i64, _p]),
     "dynb_bincount_i64": (_i32, [_p, _i64, _i64, _p, _p, _p]),

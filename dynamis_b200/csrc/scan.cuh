@@ -1,5 +1,7 @@
-// Device-wide exclusive prefix sum in three launches (tile sums, scan of the sums, apply).
-// No block ever waits on another block, so there is no spin-wait anywhere.
+// Device-wide exclusive prefix sum in two launches: tile sums, then every block adds up the sums of the
+// tiles before its own (a few hundred values out of L2) and scans its tile.  A separate one-block launch
+// scans the tile sums only when there are very many tiles.  No block ever waits on another block, so
+// there is no spin-wait anywhere.
 //
 // The element count may live on the device (`n_dev`): cell grids are sized by a kernel, and
 // reading the count back would cost a host synchronisation.  `n_host` is then only the upper
@@ -148,6 +150,73 @@ scan_apply_pair_kernel(const TIn* in0, TOut* out0, const TIn* in1, TOut* out1, c
     scan_apply_body<TIn, TOut>(blockIdx.y ? in1 : in0, n_dev, n_host, sums + (size_t)blockIdx.y * gridDim.x, blockIdx.y ? out1 : out0);
 }
 
+// sum of sums[0 .. blockIdx.x) by the whole block (and, from the last block, the grand total)
+template <typename TOut>
+__device__ __forceinline__ TOut scan_prefix_of_sums(const TOut* __restrict__ sums, int num_tiles, TOut* __restrict__ total_out)
+{
+    __shared__ TOut part[SCAN_THREADS / 32];
+    __shared__ TOut result;
+    const int mine = blockIdx.x;
+    TOut s = 0;
+    for (int i = threadIdx.x; i < mine; i += SCAN_THREADS) s += sums[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        TOut t = 0;
+#pragma unroll
+        for (int w = 0; w < SCAN_THREADS / 32; w++) t += part[w];
+        result = t;
+        if (total_out != nullptr && mine == num_tiles - 1) *total_out = t + sums[mine];
+    }
+    __syncthreads();
+    return result;
+}
+
+template <typename TIn, typename TOut>
+__device__ __forceinline__ void scan_apply_fused_body(const TIn* in, const uint32_t* __restrict__ n_dev, int64_t n_host,
+                                                      const TOut* __restrict__ sums, int num_tiles, TOut* out, TOut* total_out)
+{
+    __shared__ TOut warp_sums[SCAN_THREADS / 32];
+    const TOut before = scan_prefix_of_sums<TOut>(sums, num_tiles, total_out);
+    const int64_t n = scan_count(n_dev, n_host);
+    const int64_t base = (int64_t)blockIdx.x * SCAN_TILE + (int64_t)threadIdx.x * SCAN_ITEMS;
+    TOut v[SCAN_ITEMS];
+    TOut s = 0;
+#pragma unroll
+    for (int i = 0; i < SCAN_ITEMS; i++) {
+        v[i] = (base + i < n) ? (TOut)in[base + i] : (TOut)0;
+        s += v[i];
+    }
+    TOut tot;
+    TOut run = block_excl_scan<TOut>(s, &tot, warp_sums) + before;
+#pragma unroll
+    for (int i = 0; i < SCAN_ITEMS; i++) {
+        if (base + i < n) out[base + i] = run;
+        run += v[i];
+    }
+}
+
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(SCAN_THREADS)
+scan_apply_fused_kernel(const TIn* in, const uint32_t* __restrict__ n_dev, int64_t n_host, const TOut* __restrict__ sums,
+                        TOut* out, TOut* total_out)
+{
+    scan_apply_fused_body<TIn, TOut>(in, n_dev, n_host, sums, gridDim.x, out, total_out);
+}
+
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(SCAN_THREADS)
+scan_apply_fused_pair_kernel(const TIn* in0, TOut* out0, TOut* total0, const TIn* in1, TOut* out1, TOut* total1,
+                             const uint32_t* __restrict__ n_dev, int64_t n_host, const TOut* __restrict__ sums)
+{
+    scan_apply_fused_body<TIn, TOut>(blockIdx.y ? in1 : in0, n_dev, n_host, sums + (size_t)blockIdx.y * gridDim.x, gridDim.x,
+                                     blockIdx.y ? out1 : out0, blockIdx.y ? total1 : total0);
+}
+
+constexpr int SCAN_FUSED_MAX_TILES = 8192;  // above this the per-block summing of earlier tiles stops being negligible
+
 static inline int scan_num_tiles(int64_t n_host) { return (int)((n_host + SCAN_TILE - 1) / SCAN_TILE); }
 
 // `sums` must hold scan_num_tiles(n_host) elements of TOut.  `total_out` (device, may be null)
@@ -162,8 +231,12 @@ static inline cudaError_t exclusive_scan(const TIn* in, TOut* out, const uint32_
     }
     const int tiles = scan_num_tiles(n_host);
     scan_tile_sums_kernel<TIn, TOut><<<tiles, SCAN_THREADS, 0, stream>>>(in, n_dev, n_host, sums);
-    scan_sums_kernel<TOut><<<1, SCAN_THREADS, 0, stream>>>(sums, tiles, total_out);
-    scan_apply_kernel<TIn, TOut><<<tiles, SCAN_THREADS, 0, stream>>>(in, n_dev, n_host, sums, out);
+    if (tiles <= SCAN_FUSED_MAX_TILES) {
+        scan_apply_fused_kernel<TIn, TOut><<<tiles, SCAN_THREADS, 0, stream>>>(in, n_dev, n_host, sums, out, total_out);
+    } else {
+        scan_sums_kernel<TOut><<<1, SCAN_THREADS, 0, stream>>>(sums, tiles, total_out);
+        scan_apply_kernel<TIn, TOut><<<tiles, SCAN_THREADS, 0, stream>>>(in, n_dev, n_host, sums, out);
+    }
     return cudaGetLastError();
 }
 
@@ -176,8 +249,13 @@ static inline cudaError_t exclusive_scan_pair(const TIn* in0, TOut* out0, TOut* 
     if (n_host <= 0) return cudaSuccess;
     const int tiles = scan_num_tiles(n_host);
     scan_tile_sums_pair_kernel<TIn, TOut><<<dim3(tiles, 2), SCAN_THREADS, 0, stream>>>(in0, in1, n_dev, n_host, sums);
-    scan_sums_pair_kernel<TOut><<<2, SCAN_THREADS, 0, stream>>>(sums, tiles, total0, total1);
-    scan_apply_pair_kernel<TIn, TOut><<<dim3(tiles, 2), SCAN_THREADS, 0, stream>>>(in0, out0, in1, out1, n_dev, n_host, sums);
+    if (tiles <= SCAN_FUSED_MAX_TILES) {
+        scan_apply_fused_pair_kernel<TIn, TOut><<<dim3(tiles, 2), SCAN_THREADS, 0, stream>>>(in0, out0, total0, in1, out1, total1, n_dev,
+                                                                                          n_host, sums);
+    } else {
+        scan_sums_pair_kernel<TOut><<<2, SCAN_THREADS, 0, stream>>>(sums, tiles, total0, total1);
+        scan_apply_pair_kernel<TIn, TOut><<<dim3(tiles, 2), SCAN_THREADS, 0, stream>>>(in0, out0, in1, out1, n_dev, n_host, sums);
+    }
     return cudaGetLastError();
 }
 

@@ -666,6 +666,46 @@ static int sfc_keys_into(const float* pos, int64_t n, int curve, unsigned char* 
     return DYNB_OK;
 }
 
+
+// ------------------------------------------------------------------------------------------ pieces for a partition
+// whose atoms are spread over several ranks: bounds as plain floats (to be min/max-reduced between the
+// ranks), keys against given bounds, labels from agreed split points
+__global__ void sfc_bounds_to_float_kernel(const SfcBounds* __restrict__ b, float* __restrict__ minmax)
+{
+    if (threadIdx.x < 3) minmax[threadIdx.x] = unordered_f32(b->mn[threadIdx.x]);
+    else if (threadIdx.x < 6) minmax[threadIdx.x] = unordered_f32(b->mx[threadIdx.x - 3]);
+}
+
+__global__ void sfc_bounds_from_float_kernel(const float* __restrict__ minmax, SfcBounds* __restrict__ b)
+{
+    if (threadIdx.x < 3) b->mn[threadIdx.x] = ordered_u32(minmax[threadIdx.x]);
+    else if (threadIdx.x < 6) b->mx[threadIdx.x - 3] = ordered_u32(minmax[threadIdx.x]);
+}
+
+// labels[i] = number of split points (K_s, G_s) <= (keys[i], ids[i]) in lexicographic order; the split
+// points are sorted ascending.
+__global__ void __launch_bounds__(256)
+label_by_splits_kernel(const int64_t* __restrict__ keys, const int64_t* __restrict__ ids, int64_t n,
+                       const int64_t* __restrict__ split_keys, const int64_t* __restrict__ split_ids, int nsplit,
+                       int64_t* __restrict__ labels)
+{
+    __shared__ unsigned long long sk[SEL_MAX_SPLITS];
+    __shared__ long long sg[SEL_MAX_SPLITS];
+    for (int s = threadIdx.x; s < nsplit; s += blockDim.x) { sk[s] = (unsigned long long)split_keys[s]; sg[s] = split_ids[s]; }
+    __syncthreads();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const unsigned long long k = (unsigned long long)keys[i];
+        const long long g = ids[i];
+        int lo = 0, hi = nsplit;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            const bool le = sk[mid] < k || (sk[mid] == k && sg[mid] <= g);
+            if (le) lo = mid + 1; else hi = mid;
+        }
+        labels[i] = lo;
+    }
+}
+
 }  // namespace dynb
 
 using namespace dynb;
@@ -687,6 +727,55 @@ extern "C" int dynb_sfc_keys(const float* pos_dev, int64_t n_atoms, int curve_ty
     if (workspace_bytes < L.total) return fail_arg("workspace too small (see dynb_sfc_workspace_bytes)");
     return sfc_keys_into(pos_dev, n_atoms, curve_type, static_cast<unsigned char*>(workspace_dev), L,
                          reinterpret_cast<uint64_t*>(keys_dev), nullptr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dynb_sfc_minmax(const float* pos_dev, int64_t n_atoms, float* minmax_dev, void* stream)
+{
+    if (n_atoms < 0 || minmax_dev == nullptr) return fail_arg("bad arguments");
+    if (n_atoms > 0 && pos_dev == nullptr) return fail_arg("null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // the 24 bytes behind the six floats are the scratch for the ordered-integer extrema
+    SfcBounds* b = reinterpret_cast<SfcBounds*>(minmax_dev + 8);
+    DYNB_CUDA_OK(cudaMemsetAsync(b->mn, 0xff, sizeof(b->mn), s));
+    DYNB_CUDA_OK(cudaMemsetAsync(b->mx, 0, sizeof(b->mx), s));
+    if (n_atoms > 0) {
+        const int grid = (int)std::min<int64_t>((n_atoms + 255) / 256, (int64_t)sm_count_cached() * 4);
+        sfc_minmax_kernel<<<grid, 256, 0, s>>>(pos_dev, n_atoms, b);
+    }
+    sfc_bounds_to_float_kernel<<<1, 32, 0, s>>>(b, minmax_dev);
+    DYNB_CUDA_OK(cudaGetLastError());
+    return DYNB_OK;
+}
+
+extern "C" int dynb_sfc_keys_from_bounds(const float* pos_dev, int64_t n_atoms, int curve_type, float* minmax_dev,
+                                         int64_t* keys_dev, void* stream)
+{
+    if (n_atoms < 0 || (curve_type != 0 && curve_type != 1)) return fail_arg("curve_type must be 0 (Morton) or 1 (Hilbert)");
+    if (minmax_dev == nullptr) return fail_arg("null pointer");
+    if (n_atoms == 0) return DYNB_OK;
+    if (pos_dev == nullptr || keys_dev == nullptr) return fail_arg("null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    SfcBounds* b = reinterpret_cast<SfcBounds*>(minmax_dev + 8);
+    sfc_bounds_from_float_kernel<<<1, 32, 0, s>>>(minmax_dev, b);
+    const unsigned nbk = (unsigned)((n_atoms + 255) / 256);
+    if (curve_type == 0) sfc_keys_kernel<0><<<nbk, 256, 0, s>>>(pos_dev, n_atoms, b, reinterpret_cast<uint64_t*>(keys_dev), nullptr);
+    else sfc_keys_kernel<1><<<nbk, 256, 0, s>>>(pos_dev, n_atoms, b, reinterpret_cast<uint64_t*>(keys_dev), nullptr);
+    DYNB_CUDA_OK(cudaGetLastError());
+    return DYNB_OK;
+}
+
+extern "C" int dynb_label_by_splits(const int64_t* keys_dev, const int64_t* ids_dev, int64_t n, const int64_t* split_keys_dev,
+                                    const int64_t* split_ids_dev, int n_splits, int64_t* labels_dev, void* stream)
+{
+    if (n < 0 || n_splits < 0 || n_splits > SEL_MAX_SPLITS) return fail_arg("bad arguments");
+    if (n == 0) return DYNB_OK;
+    if (keys_dev == nullptr || ids_dev == nullptr || labels_dev == nullptr || (n_splits > 0 && (split_keys_dev == nullptr || split_ids_dev == nullptr)))
+        return fail_arg("null pointer");
+    const int grid = (int)std::min<int64_t>((n + 255) / 256, (int64_t)sm_count_cached() * 8);
+    label_by_splits_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(keys_dev, ids_dev, n, split_keys_dev, split_ids_dev,
+                                                                             n_splits, labels_dev);
+    DYNB_CUDA_OK(cudaGetLastError());
+    return DYNB_OK;
 }
 
 extern "C" int dynb_sfc_partition(const float* pos_dev, int64_t n_atoms, const int64_t* weights_dev, int64_t W, int curve_type,

@@ -125,6 +125,20 @@ int dynb_sfc_partition(const float* pos_dev, int64_t n_atoms, const int64_t* wei
 /* Keys alone, in atom order (sfc_kernels.cu:32-109). */
 int dynb_sfc_keys(const float* pos_dev, int64_t n_atoms, int curve_type, int64_t* keys_dev, void* workspace_dev,
                   int64_t workspace_bytes, void* stream);
+/* The same partition when the atoms are spread over several ranks and no rank holds them all (the
+ * reference gathers every atom to every rank first, dynamis/src/dynamis/simulatorState.py:136-199, then
+ * calls sfc_partition_cuda): dynb_sfc_minmax gives this rank's coordinate extrema as six floats
+ * (min xyz, max xyz) for the caller to min/max-reduce between the ranks; dynb_sfc_keys_from_bounds
+ * computes the keys of this rank's atoms against the reduced extrema (sfc_kernels.cu:32-109, same
+ * arithmetic); dynb_label_by_splits labels an atom with the number of split points (key, global id) that
+ * are <= its own (key, global id) — the split points being the atoms at the sorted positions where the
+ * reference's closed form (sfc_kernels.cu:114-137) starts a new label, found by the ranks together.
+ * minmax_dev: 32 floats; the first six carry the extrema, the rest is scratch. */
+int dynb_sfc_minmax(const float* pos_dev, int64_t n_atoms, float* minmax_dev, void* stream);
+int dynb_sfc_keys_from_bounds(const float* pos_dev, int64_t n_atoms, int curve_type, float* minmax_dev, int64_t* keys_dev,
+                              void* stream);
+int dynb_label_by_splits(const int64_t* keys_dev, const int64_t* ids_dev, int64_t n, const int64_t* split_keys_dev,
+                         const int64_t* split_ids_dev, int n_splits, int64_t* labels_dev, void* stream);
 /* Stable LSD radix sort of (uint64 key, uint32 value) pairs on key bits [begin_bit, end_bit), in
  * place (replaces the at::sort call at sfc_kernels.cu:224). */
 int dynb_radix_sort_workspace_bytes(int64_t n, int64_t* bytes);
