@@ -406,8 +406,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="fcc", choices=["fcc", "liquid"],
-                    help="N > 1 only: fcc = 8,001,504-atom fcc Cu cut into N subdomains (strong scaling), liquid = N x 1,000,000 atoms")
+    ap.add_argument("--workload", default="fcc", choices=["fcc", "liquid", "migrate"],
+                    help="N > 1 only: fcc = 8,001,504-atom fcc Cu cut into N subdomains (strong scaling), liquid = N x 1,000,000 atoms, "
+                         "migrate = 4,000,000 drifting atoms with repartition and migration (reports milliseconds per repartition)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="N > 1 only: one-sided peer stores or NCCL all-to-all")
     ap.add_argument("--ce-threshold", type=int, default=0, help="N > 1, peer exchange: copy-engine threshold in bytes (0 = SM stores)")
     args = ap.parse_args()

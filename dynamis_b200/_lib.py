@@ -108,7 +108,7 @@ SIGNATURES = {
     "dynb_halo_forward_begin": (_i32, [_p, _p, _i64, _i64, _p, _i64, _p, _u32, _u32, _i32, _p]),
     "dynb_halo_forward_end": (_i32, [_p, _u32, _i64, _p, _p, _i64, _p]),
     "dynb_halo_backward_begin": (_i32, [_p, _p, _i64, _i64, _i64, _p, _p, _u32, _p]),
-    "dynb_halo_backward_end": (_i32, [_p, _u32, _i64, _p, _p, _i64, _i64, _i32, _p, _p, _p, _p, _p]),
+    "dynb_halo_backward_end": (_i32, [_p, _u32, _i64, _p, _p, _p, _i64, _i64, _i32, _p, _p, _p, _p, _p]),
     "dynb_halo_signal": (_i32, [_p, _i32, _u32, _u32, _p]),
     "dynb_halo_wait": (_i32, [_p, _i32, _u32, _i64, _p]),
     "dynb_host_alloc_mapped": (_i32, [_i64, ctypes.POINTER(_p), ctypes.POINTER(_p)]),

@@ -103,6 +103,8 @@ class _ReversePlan:
             recv = self.inv_offsets[1:] > self.inv_offsets[:-1]
             self.rows = torch.nonzero(recv).reshape(-1).contiguous()
             self.has_recv = recv.to(torch.uint8).contiguous()
+            # first received row of every listed row (read next to the row id instead of behind two more loads)
+            self.row_first = self.inv_entries[self.inv_offsets[self.rows]].contiguous() if self.rows.numel() else self.inv_entries[:0]
         self.n_local = n_local
 
     def apply(self, grad: torch.Tensor, recv_ptr: int, out: torch.Tensor) -> None:
@@ -641,7 +643,7 @@ class FeatureExchanger:
         rv = self.reverse
         with torch.cuda.device(self.device):
             _lib.check(_lib.lib().dynb_halo_backward_end(self._ctx.ref(), gen, self.wait_ns, g.data_ptr(), rv.rows.data_ptr(),
-                                                         rv.rows.numel(), self.F, _DT[self.dtype],
+                                                         rv.row_first.data_ptr(), rv.rows.numel(), self.F, _DT[self.dtype],
                                                          self._alloc.ptr + self.layout["grad_off"][gen & 1],
                                                          rv.inv_offsets.data_ptr(), rv.inv_entries.data_ptr(), out.data_ptr(),
                                                          _stream(self.device)), "halo_backward_end")

@@ -286,10 +286,13 @@ int dynb_halo_forward_end(const dynb_halo_ctx* ctx, uint32_t gen, int64_t timeou
 int dynb_halo_backward_begin(const dynb_halo_ctx* ctx, const void* grad_dev, int64_t n_local, int64_t n_ghost,
                              int64_t row_bytes, const uint8_t* has_recv_dev, void* out_dev, uint32_t gen, void* stream);
 /* Reverse, second half: bounded wait, drift OR, then out[row] = grad[row] + the received rows naming row
- * (inverse CSR of dynb_inverse_csr, fixed order, no atomics) for the n_rows rows listed in rows_dev. */
+ * (inverse CSR of dynb_inverse_csr, fixed order, no atomics) for the n_rows rows listed in rows_dev.
+ * row_first_dev (optional, may be NULL): inv_entries[inv_offsets[rows[r]]] for every listed row r, which
+ * shortens the chain of dependent loads in front of the row data. */
 int dynb_halo_backward_end(const dynb_halo_ctx* ctx, uint32_t gen, int64_t timeout_ns, const void* grad_dev,
-                           const int64_t* rows_dev, int64_t n_rows, int64_t feature_dim, int dtype, const void* recv_dev,
-                           const int64_t* inv_offsets_dev, const uint32_t* inv_entries_dev, void* out_dev, void* stream);
+                           const int64_t* rows_dev, const uint32_t* row_first_dev, int64_t n_rows, int64_t feature_dim,
+                           int dtype, const void* recv_dev, const int64_t* inv_offsets_dev, const uint32_t* inv_entries_dev,
+                           void* out_dev, void* stream);
 /* A handshake without rows (record_push_complete / wait_for_pushes as stand-alone calls,
  * ipc_exchanger.cpp:784-828): the signal carries the drift word (flag copied before the counter write,
  * :788-796), the wait ORs all ranks' words into drift_global (watchdog_or_kernel,
