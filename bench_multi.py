@@ -152,12 +152,89 @@ def run_migrate(args, rank: int, world: int, dev: torch.device):
     dist.destroy_process_group()
 
 
+def run_exchange_parts(args, rank: int, world: int, dev: torch.device):
+    """--workload exchange: the pieces of one forward halo push timed apart, on synthetic plans of the size
+    of the fcc workload (per rank n_local rows of F = 128 floats, `send` rows spread evenly over the peers):
+    stores into the peers alone, the copy of the own rows alone, both in one launch (the product), and the
+    copy-engine route (pack kernel + one peer copy per rank).  CUDA events, median, max over ranks."""
+    import ctypes  # noqa: F401
+
+    import dynamis_b200 as D
+    from dynamis_b200 import _lib
+
+    n_local = 8_001_504 // world
+    per = 395_000 // (world - 1)
+    n_send, F = per * (world - 1), F_EMB
+    rng = np.random.default_rng(rank)
+    sl = np.concatenate([np.sort(rng.choice(n_local, per, replace=False)) for _ in range(world - 1)])
+    cnt = np.array([0 if p == rank else per for p in range(world)])
+    so = np.concatenate([[0], np.cumsum(cnt)]).astype(np.int64)
+    e = D.FeatureExchanger(result_ring=0)
+    meta = e.local_setup(torch.as_tensor(so), torch.as_tensor(sl), torch.as_tensor(so.copy()), n_local, F, rank, world, dev)
+    metas = [None] * world
+    dist.all_gather_object(metas, meta)
+    e.connect(metas)
+    x = torch.randn(n_local, F, device=dev)
+    out = torch.empty(n_local + n_send, F, device=dev)
+    stage = torch.empty(n_send, F, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    L, rb = _lib.lib(), F * 4
+    st = torch.cuda.current_stream(dev).cuda_stream
+
+    def timed(fn):
+        ts = []
+        for _ in range(max(args.steps, 5)):
+            flush.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        t = torch.tensor([float(np.median(ts))], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    def begin(head: bool, skip: int):
+        e._gen[0] += 1
+        _lib.check(L.dynb_halo_forward_begin(e._ctx.ref(), x.data_ptr(), n_local, rb, e.send_local.data_ptr(), e.total_send,
+                                             out.data_ptr() if head else None, e._gen[0], 0, skip, st), "halo_forward_begin")
+        _lib.check(L.dynb_halo_forward_end(e._ctx.ref(), e._gen[0], e.wait_ns, None, None, 0, st), "halo_forward_end")
+
+    def pack():
+        _lib.check(L.dynb_pack_rows(x.data_ptr(), n_local, rb, e.send_local.data_ptr(), n_send, stage.data_ptr(), None, st), "pack_rows")
+
+    def peer_copies():
+        for r in e._peer_recs:
+            if r.remote_base:
+                _lib.check(L.dynb_copy_async(r.remote_base + r.fwd_stage_off[0] + r.fwd_row_offset * rb,
+                                             stage.data_ptr() + r.send_start * rb, r.send_count * rb, st), "copy_async")
+
+    res = {"push_only_ms": timed(lambda: begin(False, 0)), "copy_only_ms": timed(lambda: begin(True, 1)),
+           "push_and_copy_ms": timed(lambda: begin(True, 0)), "pack_ms": timed(pack), "peer_copies_ms": timed(peer_copies)}
+    e.check_status()
+    if rank == 0:
+        mb = n_send * rb / 1e6
+        print(json.dumps({"metric": "halo_push_parts_ms", "n_gpus": world, "rows_local": n_local, "rows_sent": n_send, "F": F,
+                          "payload_mb_per_rank": mb, "copy_gb_per_rank": 2 * n_local * rb / 1e9, **res,
+                          "push_only_gbs": mb / res["push_only_ms"], "peer_copies_gbs": mb / res["peer_copies_ms"],
+                          "timing": "CUDA events on each rank's stream, L2 flushed, median, max over ranks; each piece is "
+                                    "followed by the bounded wait for all peers' signals where it signals"}), flush=True)
+    dist.barrier()
+    e.teardown()
+    dist.destroy_process_group()
+
+
 def run(args, rank: int, world: int, dev: torch.device):
     import dynamis_b200 as D
     from dynamis_b200 import synthetic
 
     if args.workload == "migrate":
         return run_migrate(args, rank, world, dev)
+    if args.workload == "exchange":
+        return run_exchange_parts(args, rank, world, dev)
     K, Wm = args.steps, max(args.warmup, 3)
     if args.workload == "liquid":
         n_total = B.ATOMS_PER_GPU * world
