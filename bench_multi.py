@@ -86,12 +86,11 @@ def run_migrate(args, rank: int, world: int, dev: torch.device):
         return (time.perf_counter() - t0) * 1e3
 
     first_ms = timed(st.repartition)                                          # nearly every atom changes owner
-    ex = [D.GPUDirectExchanger() for _ in range(layers)]
+    ex = [D.GPUDirectExchanger(headroom=0.25) for _ in range(layers)]
 
     def setup():
-        for x in ex:
-            if x.is_ipc_setup:
-                x.reset_buffers()
+        # with head-room the exchangers keep their peer-visible allocation and the peers' mappings of it while the
+        # new plan fits: a rebuild then costs one metadata exchange per exchanger
         for x in ex:
             x.setup_exchanger(F, st.local_partition_info, dev)
             x.is_ipc_setup = True

@@ -123,6 +123,7 @@ SIGNATURES = {
     "dynb_ipc_close": (_i32, [_p]),
     "dynb_enable_peer_access": (_i32, [_i32]),
     "dynb_copy_async": (_i32, [_p, _p, _i64, _p]),
+    "dynb_fill_zero": (_i32, [_p, _i64, _p]),
     "dynb_scatter_rows": (_i32, [_p, _i64, _p, _i64, _i64, _p, _p, _p]),
     "dynb_drift_flag": (_i32, [_p, _p, _p, _p, _i64, _f64, _f64, _p, _p, _p]),
     "dynb_kdtree_workspace_bytes": (_i32, [_i64, _i64, ctypes.POINTER(_i64)]),

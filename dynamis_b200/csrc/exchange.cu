@@ -856,6 +856,15 @@ extern "C" int dynb_copy_async(void* dst_dev, const void* src_dev, int64_t bytes
     return DYNB_OK;
 }
 
+extern "C" int dynb_fill_zero(void* dst_dev, int64_t bytes, void* stream)
+{
+    if (bytes < 0) return fail_arg("bad arguments");
+    if (bytes == 0) return DYNB_OK;
+    if (dst_dev == nullptr) return fail_arg("null pointer");
+    DYNB_CUDA_OK(cudaMemsetAsync(dst_dev, 0, (size_t)bytes, static_cast<cudaStream_t>(stream)));
+    return DYNB_OK;
+}
+
 extern "C" int dynb_enable_peer_access(int peer_device)
 {
     int dev = 0;

@@ -220,19 +220,23 @@ def _open_handle(handle, device: torch.device) -> int:
     return q.value
 
 
-def exchange_layout(n_local: int, total_recv: int, total_send: int, row_bytes: int, world_size: int, ring: int) -> dict:
+def exchange_layout(n_local: int, total_recv: int, total_send: int, row_bytes: int, world_size: int, ring: int,
+                    capacity: Optional[Tuple[int, int, int]] = None) -> dict:
     """Byte offsets inside a rank's exchange allocation; a pure function of the sizes, so that a rank
-    can also derive its peers' layouts from their sizes alone."""
-    slot = _align(max(n_local + total_recv, 1) * row_bytes)
-    stage = _align(max(total_recv, 1) * row_bytes)
-    grad = _align(max(total_send, 1) * row_bytes)
+    can also derive its peers' layouts from their sizes alone.  ``capacity`` = (result rows, ghost rows,
+    sent rows) the regions are sized for, when they are to outlive a change of the halo plan."""
+    cap_rows, cap_recv, cap_send = capacity if capacity is not None else (n_local + total_recv, total_recv, total_send)
+    slot = _align(max(cap_rows, 1) * row_bytes)
+    stage = _align(max(cap_recv, 1) * row_bytes)
+    grad = _align(max(cap_send, 1) * row_bytes)
     ring_off = 0
     stage_off = ring * slot
     grad_off = stage_off + 2 * stage
     flags_off = grad_off + 2 * grad
     return {"ring": ring, "ring_off": ring_off, "slot_bytes": slot, "ring_tail": ring_off + n_local * row_bytes,
             "stage_off": [stage_off, stage_off + stage], "grad_off": [grad_off, grad_off + grad], "flags_off": flags_off,
-            "total": flags_off + _align(3 * 2 * world_size * 16)}
+            "flags_bytes": _align(3 * 2 * world_size * 16), "total": flags_off + _align(3 * 2 * world_size * 16),
+            "capacity": [int(cap_rows), int(cap_recv), int(cap_send)]}
 
 
 class _HaloContext:
@@ -325,10 +329,12 @@ class FeatureExchanger:
         self._ctx: Optional[_HaloContext] = None
         self._setup = False
         self._opened: List[int] = []
+        self._mapped: Dict[bytes, int] = {}   # peers' allocations already mapped, by handle
         self._gen = [0, 0, 0]  # forward, backward, bare handshake
         self._wired = None
         self._ce_threshold = 0
         self._compat = None
+        self.layout = None
 
     # -- reference-compatible small surface
     def is_ipc_setup(self) -> bool:
@@ -375,32 +381,62 @@ class FeatureExchanger:
 
     # -- setup
     def local_setup(self, send_offsets, send_local_indices, recv_offsets, num_local: int, feature_dim: int, rank: int,
-                    world_size: int, device: torch.device, dtype: torch.dtype = torch.float32) -> dict:
+                    world_size: int, device: torch.device, dtype: torch.dtype = torch.float32, headroom: float = 0.0) -> dict:
+        """Allocates (or keeps) this rank's exchange allocation for the given halo plan and returns the record
+        the peers need.  ``headroom`` > 0 sizes the regions for (1 + headroom) x the plan; a later call whose
+        plan still fits — same rank, world, row type — keeps the allocation and the peers' mappings of it, so
+        that a halo rebuild costs a metadata exchange instead of allocating and mapping gigabytes again.  Every
+        rank must call it at the same point of the push sequence; the generation counters start over."""
         if dtype not in _DT:
             raise RuntimeError("FeatureExchanger supports float32 and float64 rows")
-        if self._setup or self._alloc is not None:
-            self.teardown()
-        self.device = torch.device(device)
-        self.rank, self.W = int(rank), int(world_size)
-        if not 1 <= self.W <= 128:
-            raise RuntimeError("FeatureExchanger supports 1 to 128 ranks")
-        self.n_local, self.F, self.dtype = int(num_local), int(feature_dim), dtype
-        self.row_bytes = self.F * torch.empty((), dtype=dtype).element_size()
+        device = torch.device(device)
         so = [int(v) for v in send_offsets.tolist()]
         ro = [int(v) for v in recv_offsets.tolist()]
-        if len(so) != self.W + 1 or len(ro) != self.W + 1:
+        W = int(world_size)
+        if not 1 <= W <= 128:
+            raise RuntimeError("FeatureExchanger supports 1 to 128 ranks")
+        if len(so) != W + 1 or len(ro) != W + 1:
             raise RuntimeError("send_offsets / recv_offsets must have world_size + 1 entries")
+        row_bytes = int(feature_dim) * torch.empty((), dtype=dtype).element_size()
+        n_local, total_send, total_recv = int(num_local), so[-1], ro[-1]
+        keep = (self._alloc is not None and self._alloc.ptr is not None and getattr(self, "layout", None) is not None
+                and self.device == device and self.rank == int(rank) and self.W == W and self.row_bytes == row_bytes
+                and self.dtype == dtype and self.layout["ring"] == self.ring
+                and n_local + total_recv <= self.layout["capacity"][0] and total_recv <= self.layout["capacity"][1]
+                and total_send <= self.layout["capacity"][2])
+        if not keep and (self._setup or self._alloc is not None):
+            self.teardown()
+        self.device = device
+        self.rank, self.W = int(rank), W
+        self.n_local, self.F, self.dtype = n_local, int(feature_dim), dtype
+        self.row_bytes = row_bytes
         self.send_offsets_h, self.recv_offsets_h = so, ro
-        self.total_send, self.total_recv = so[-1], ro[-1]
+        self.total_send, self.total_recv = total_send, total_recv
         self.send_local = send_local_indices.to(device=self.device, dtype=torch.int64).contiguous()
         if self.send_local.numel() != self.total_send:
             raise RuntimeError("send_local_indices length does not match send_offsets")
-        self.layout = exchange_layout(self.n_local, self.total_recv, self.total_send, self.row_bytes, self.W, self.ring)
-        self._alloc = _IpcAllocation(self.layout["total"], self.device)
+        if keep:
+            cap = tuple(self.layout["capacity"])
+            self.layout = exchange_layout(n_local, total_recv, total_send, row_bytes, W, self.ring, cap)
+            with torch.cuda.device(self.device):
+                torch.cuda.synchronize(self.device)
+                # the handshake records start over with the generation counters
+                _lib.check(_lib.lib().dynb_fill_zero(self._alloc.ptr + self.layout["flags_off"], self.layout["flags_bytes"],
+                                                     _stream(self.device)), "fill_zero")
+                torch.cuda.synchronize(self.device)
+            self._setup = False
+        else:
+            cap = None
+            if headroom > 0:
+                grow = lambda v: int(v * (1.0 + headroom)) + 1024  # noqa: E731
+                cap = (grow(n_local + total_recv), grow(total_recv), grow(total_send))
+            self.layout = exchange_layout(n_local, total_recv, total_send, row_bytes, W, self.ring, cap)
+            self._alloc = _IpcAllocation(self.layout["total"], self.device)
+            self._handle = self._alloc.handle()
         with torch.cuda.device(self.device):
             self.reverse = _ReversePlan(self.send_local, self.n_local)
         return {
-            "rank": self.rank, "pid": os.getpid(), "ptr": self._alloc.ptr, "handle": self._alloc.handle(),
+            "rank": self.rank, "pid": os.getpid(), "ptr": self._alloc.ptr, "handle": self._handle,
             "device": self.device.index, "layout": self.layout, "send_offsets": so, "recv_offsets": ro,
             "num_local": self.n_local, "row_bytes": self.row_bytes,
         }
@@ -425,8 +461,11 @@ class FeatureExchanger:
                     if m["device"] != self.device.index:
                         _lib.check(L.dynb_enable_peer_access(int(m["device"])), "enable_peer_access")
                 else:
-                    base = _open_handle(m["handle"], self.device)
-                    self._opened.append(base)
+                    base = self._mapped.get(m["handle"])
+                    if base is None:
+                        base = _open_handle(m["handle"], self.device)
+                        self._mapped[m["handle"]] = base
+                        self._opened.append(base)
                 lay = m["layout"]
                 cnt = self.send_offsets_h[p + 1] - self.send_offsets_h[p]
                 theirs = m["recv_offsets"][self.rank + 1] - m["recv_offsets"][self.rank]
@@ -448,12 +487,15 @@ class FeatureExchanger:
                 rec.recv_start, rec.recv_count = self.recv_offsets_h[p], cntb
                 peers.append(rec)
             self._peer_recs = peers
+            if self._ctx is not None:
+                self._ctx.close()
             self._ctx = _HaloContext(self.device, self.rank, self.W, self._alloc.ptr, self.layout["flags_off"], peers, self.wait_ns)
             if self._wired is not None:
                 self._ctx.set_drift(*self._wired)
         self._gen = [0, 0, 0]
         self._announced = 0          # where this generation's ghost rows were told to go: 0 staging, s + 1 slot s
-        self._slot_refs = [None] * self.ring
+        if len(getattr(self, "_slot_refs", [])) != self.ring:
+            self._slot_refs = [None] * self.ring     # kept across a re-plan: results still held keep their slots busy
         self._pending: Dict[int, int] = {}
         self._ce_stage = None
         self._setup = True
@@ -522,10 +564,13 @@ class FeatureExchanger:
                 for q in self._opened:
                     L.dynb_ipc_close(q)
                 self._opened = []
+                self._mapped = {}
             if self._ctx is not None:
                 self._ctx.close()
             # tensors handed out over result slots keep the allocation alive; it is freed with the last of them
             self._alloc = None
+            self.layout = None
+            self._slot_refs = []
         self._ctx = None
         self._compat = None
         self._setup = False
@@ -972,9 +1017,10 @@ class PythonNCCLExchanger(Exchanger):
 class GPUDirectExchanger(Exchanger):
     """One-sided NVLink push (wraps FeatureExchanger; metadata travels through torch.distributed)."""
 
-    def __init__(self, group=None, wait_ns: int = DEFAULT_WAIT_NS, result_ring: int = 3) -> None:
+    def __init__(self, group=None, wait_ns: int = DEFAULT_WAIT_NS, result_ring: int = 3, headroom: float = 0.0) -> None:
         super().__init__()
         self.group = group
+        self.headroom = float(headroom)   # > 0: set_up again for a new halo plan keeps allocation and mappings while it fits
         self.exchanger = FeatureExchanger(wait_ns, result_ring)
         self.is_ipc_setup = False
         self.send_buffer = None
@@ -1011,7 +1057,8 @@ class GPUDirectExchanger(Exchanger):
         rank, W = dist.get_rank(self.group), dist.get_world_size(self.group)
         n_local = len(partition_info.partition_indices)
         meta = self.exchanger.local_setup(partition_info.send_offsets, partition_info.send_local_indices,
-                                          partition_info.recv_offsets, n_local, feature_dim, rank, W, device)
+                                          partition_info.recv_offsets, n_local, feature_dim, rank, W, device,
+                                          headroom=self.headroom)
         all_meta = [None] * W
         dist.all_gather_object(all_meta, meta, group=self.group)
         self.exchanger.connect(all_meta)

@@ -323,8 +323,10 @@ int dynb_ipc_export(void* ptr, uint8_t* handle64_out);
 int dynb_ipc_open(const uint8_t* handle64, void** ptr_out);
 int dynb_ipc_close(void* ptr);
 int dynb_enable_peer_access(int peer_device);
-/* Device-to-device copy on the stream (the local rows and ghost rows of the concatenated result). */
+/* Device-to-device copy on the stream (the local rows and ghost rows of the concatenated result), and
+ * zero fill (the handshake records when an exchange allocation is kept for a new halo plan). */
 int dynb_copy_async(void* dst_dev, const void* src_dev, int64_t bytes, void* stream);
+int dynb_fill_zero(void* dst_dev, int64_t bytes, void* stream);
 
 /* ------------------------------------------------------------------ repartition / drift watchdog
  * out[idx[i], :] = rows[i, :] for unique idx: puts rows gathered from all ranks back into canonical

@@ -84,7 +84,7 @@ def main():
         pid2 = O.sfc_partition(pos, None, W, curve)
         check(st, rank, W, pos, vel, cell, [1, 1, 1], rc + buf, curve, pid2, f"{name}: second repartition")
         moved = int((pid2 != pid).sum())
-        tot = torch.tensor([st.last["atoms_leaving"]], dtype=torch.int64)
+        tot = torch.tensor([st.last["atoms_leaving"]], dtype=torch.int64, device="cpu" if shared else dev)
         dist.all_reduce(tot)
         assert int(tot) == moved, (int(tot), moved)
         # the halo plan drives a real exchange of the owned rows: ghost rows equal the owners' rows

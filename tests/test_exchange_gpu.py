@@ -293,6 +293,60 @@ def test_copy_engine_variant_matches(cuda, ring):
         e.teardown()
 
 
+def test_new_halo_plan_keeps_the_allocation_while_it_fits(cuda):
+    """local_setup with head-room: a second plan that fits keeps the exchange allocation (no new peer-visible
+    memory, no new mappings), the generations start over and the exchange is right; a plan beyond the
+    capacity allocates anew."""
+    W, F = 3, 16
+    rng = np.random.default_rng(31)
+
+    def plans_for(n, L, r):
+        pos = (rng.random((n, 3)) * L).astype(np.float32)
+        g = O.radius_graph(pos, (np.eye(3) * L).astype(np.float32), [1, 1, 1], np.float32(r))
+        pid = O.sfc_partition(pos, None, W, 0)
+        return [O.build_halo_maps(g["src"], g["dst"], pid, k, W) for k in range(W)]
+
+    def check(ex, maps):
+        so, sl, ro = [m["send_offsets"] for m in maps], [m["send_local_indices"] for m in maps], [m["recv_offsets"] for m in maps]
+        nl = [m["num_local"] for m in maps]
+        for it in range(3):
+            feats = [rng.standard_normal((m["num_local"], F)).astype(np.float32) for m in maps]
+            out = _exchange_all(ex, [torch.as_tensor(f, device=cuda) for f in feats])
+            ref = O.exchange_forward(feats, so, sl, ro)
+            for k in range(W):
+                np.testing.assert_array_equal(out[k].cpu().numpy(), ref[k])
+            grads = [rng.standard_normal(o.shape).astype(np.float32) for o in ref]
+            back = _exchange_back_all(ex, [torch.as_tensor(x, device=cuda) for x in grads])
+            refb = O.exchange_backward(grads, nl, so, sl, ro)
+            for k in range(W):
+                np.testing.assert_allclose(back[k].cpu().numpy(), refb[k], rtol=1e-6, atol=1e-6)
+            del out, back
+
+    def setup(ex, maps):
+        metas = [ex[k].local_setup(torch.as_tensor(m["send_offsets"]), torch.as_tensor(m["send_local_indices"]),
+                                   torch.as_tensor(m["recv_offsets"]), m["num_local"], F, k, W, cuda, headroom=0.5)
+                 for k, m in enumerate(maps)]
+        for e in ex:
+            e.connect(metas)
+
+    ex = [D.FeatureExchanger(5_000_000_000) for _ in range(W)]
+    a = plans_for(3000, 36.0, 6.5)
+    setup(ex, a)
+    ptrs = [e._alloc.ptr for e in ex]
+    check(ex, a)
+    b = plans_for(3300, 36.0, 6.0)           # other sizes, within the head-room
+    setup(ex, b)
+    assert [e._alloc.ptr for e in ex] == ptrs
+    check(ex, b)
+    c = plans_for(9000, 40.0, 6.5)           # beyond the capacity: new allocations
+    setup(ex, c)
+    check(ex, c)
+    assert all(e.layout["capacity"][0] >= m["num_local"] + int(m["recv_offsets"][-1]) for e, m in zip(ex, c))
+    for e in ex:
+        e.check_status()
+        e.teardown()
+
+
 def test_push_rows_skips_and_reports_rows_out_of_range(cuda):
     """dynb_push_rows with a source index outside the input and a destination row beyond the target's
     capacity: both rows are skipped (nothing is written out of bounds) and the bad word is set."""
