@@ -255,6 +255,55 @@ def reference_cuda(pos, cell, pbc, r, E):
                     "compiled for sm_100, CUDA events, median of 20 after 5 warm-up calls; edges_per_s over graph + Morton partition"}
 
 
+def run_share(args):
+    """--share-of N (one GPU): the radius graph rank 0 builds in the N-GPU fcc workload — its owned atoms as
+    targets over [owned | atoms within the halo width of their bounding box] — timed alone on one GPU, so that
+    the per-rank graph time of the multi-GPU line can be looked at kernel by kernel (launch list under ncu)."""
+    import torch
+
+    import dynamis_b200 as D
+    from dynamis_b200 import synthetic
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    K, W = args.steps, max(args.warmup, 3)
+    pos_np, cell_np, pbc_np, r = synthetic.fcc_copper(126, seed=1004)
+    pos = torch.from_numpy(pos_np).to(dev)
+    labels = D.sfc_partition_labels(pos, None, args.share_of, 0)
+    own = torch.nonzero(labels == 0).reshape(-1)
+    L = float(cell_np[0, 0])
+    lo, hi = pos[own].min(dim=0).values, pos[own].max(dim=0).values
+    d = ((pos - (lo + hi) / 2 + L / 2) % L - L / 2).abs() - (hi - lo) / 2
+    keep = (d <= r + 6.0).all(dim=1)
+    keep[own] = False
+    allpos = torch.cat([pos[own], pos[torch.nonzero(keep).reshape(-1)]]).contiguous()
+    targets = torch.arange(own.numel(), dtype=torch.int64, device=dev)
+    cell, pbc = torch.from_numpy(cell_np), torch.from_numpy(pbc_np)
+    del pos, labels, keep, d
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for _ in range(W):
+        out = D.radius_graph_pbc_ex(allpos, cell, pbc, r, 0, False, targets)
+    E = int(out[2].item())
+    del out
+    ts = []
+    for _ in range(K):
+        flush.zero_()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        out = D.radius_graph_pbc_ex(allpos, cell, pbc, r, 0, False, targets)
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+        del out
+    ms = float(np.mean(ts))
+    print(json.dumps({"metric": "radius_graph_edges_per_s", "value": E / (ms * 1e-3), "unit": "edges/s", "n_gpus": 1, "steps": K,
+                      "warmup": W, "ms_per_step": ms, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": f"fcc Cu 8,001,504 atoms, cutoff 6.0 A: rank 0's share of the {args.share_of}-GPU workload on one "
+                                             f"GPU, {own.numel()} owned atoms as targets over {allpos.shape[0]} positions",
+                                 "edges_per_step": E}}), flush=True)
+
+
 def run_ours(args):
     import torch
 
@@ -423,10 +472,14 @@ def main():
                          "migrate = 4,000,000 drifting atoms with repartition and migration (reports milliseconds per repartition), "
                          "exchange = the pieces of one forward halo push timed apart")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="N > 1 only: one-sided peer stores or NCCL all-to-all")
+    ap.add_argument("--share-of", type=int, default=0,
+                    help="one GPU: time rank 0's radius graph of the N-GPU fcc workload alone (0 = off)")
     ap.add_argument("--ce-threshold", type=int, default=0, help="N > 1, peer exchange: copy-engine threshold in bytes (0 = SM stores)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.share_of > 1 and args.gpus <= 1:
+        run_share(args)
     else:
         run_ours(args)
 

@@ -62,6 +62,7 @@ struct DevHeader {
     double res_inv;
     double clip_lo[3];  // source images outside [clip_lo, clip_hi] cannot reach any target and are dropped
     double clip_hi[3];
+    uint32_t active_groups;  // entries of the list of groups that hold targets (target subsets only)
 };
 static_assert(offsetof(DevHeader, ncell_plus1) == sizeof(dynb_rg_header), "public header prefix mismatch");
 
@@ -673,12 +674,51 @@ template <typename T> struct PairParams {
     unsigned short* hitmask;  // [Nt, 32] per lane: bit s set if candidate 32 s + lane is a neighbour (written by COUNT)
     const uint2* smeta;       // [M] {atom id, packed shift code} per source record
     int32_t* counts_out;      // [Nt] degrees in caller order, or nullptr
+    const uint32_t* glist;    // groups that hold at least one target (h->active_groups entries), or nullptr = all groups
     T r2;
 };
 // The plan stores its PairParams inside the workspace (after the header) so that the fill call
 // needs nothing but the workspace pointer.
 constexpr int64_t RG_PARAMS_OFFSET = 512;
 constexpr int64_t RG_HEADER_BYTES = 1024;
+
+// With a target subset (a rank building edges for the atoms it owns) the grid may span far more cells than
+// hold targets — a subdomain that touches the periodic boundary has wrapped targets on both sides of the box
+// and its grid covers the whole box.  The cell-scan kernels then walk a list of the groups that hold targets
+// instead of all groups.  The order of the list is not defined (it only distributes the work; every target's
+// output place is fixed by the offsets).
+template <typename T>
+__global__ void __launch_bounds__(256)
+rg_group_list_kernel(const PairParams<T>* __restrict__ params_dev, uint32_t* __restrict__ glist)
+{
+    const PairParams<T> p = *params_dev;
+    DevHeader* hp = p.h;
+    if (hp->status & RG_FATAL) return;
+    const int nx = hp->nx, ny = hp->ny, S = hp->group_cells, Sy = hp->group_cells_y;
+    const uint32_t gx = (uint32_t)hp->gx;
+    const uint32_t gy = (uint32_t)((ny + Sy - 1) / Sy);
+    const uint32_t num_groups = (uint32_t)hp->num_groups;
+    const int lane = threadIdx.x & 31;
+    for (uint32_t g0 = (blockIdx.x * blockDim.x + threadIdx.x) & ~31u; g0 < num_groups; g0 += gridDim.x * blockDim.x) {
+        const uint32_t grp = g0 + lane;
+        bool has = false;
+        if (grp < num_groups) {
+            const uint32_t row = grp / gx;
+            const int ix = (int)(grp - row * gx);
+            const int cz = (int)(row / gy), iy = (int)(row - (uint32_t)cz * gy);
+            const int cx0 = ix * S, cx1 = min(cx0 + S, nx) - 1;
+            const int cy0 = iy * Sy, cy1 = min(cy0 + Sy, ny) - 1;
+            has = p.tcstart[((uint32_t)cz * ny + cy0) * nx + cx0] != p.tcstart[((uint32_t)cz * ny + cy0) * nx + cx1 + 1];
+            if (!has && cy1 > cy0)
+                has = p.tcstart[((uint32_t)cz * ny + cy1) * nx + cx0] != p.tcstart[((uint32_t)cz * ny + cy1) * nx + cx1 + 1];
+        }
+        const uint32_t m = __ballot_sync(0xffffffffu, has);
+        uint32_t base = 0;
+        if (lane == 0 && m) base = atomicAdd(&hp->active_groups, (uint32_t)__popc(m));
+        base = __shfl_sync(0xffffffffu, base, 0);
+        if (has) glist[base + __popc(m & lanemask_lt())] = grp;
+    }
+}
 
 template <typename T, int MODE>
 __global__ void __launch_bounds__(PAIR_THREADS, 4)
@@ -705,7 +745,7 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
     const int nx = hp->nx, ny = hp->ny, nz = hp->nz, S = hp->group_cells, Sy = hp->group_cells_y, pad = hp->pad;
     const uint32_t gx = (uint32_t)hp->gx;
     const uint32_t gy = (uint32_t)((ny + Sy - 1) / Sy);
-    const uint32_t num_groups = (uint32_t)hp->num_groups;  // < 2^31: never more groups than cells
+    const uint32_t num_groups = p.glist ? hp->active_groups : (uint32_t)hp->num_groups;  // < 2^31: never more groups than cells
     const int Wd = 2 * pad + 1, Wy = Sy + 2 * pad, nrun = Wy * Wd;
     const int lane_dy = (lane % Wy) - pad, lane_dz = (lane / Wy) - pad;
     const T r2 = p.r2;
@@ -713,7 +753,8 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
     const uint32_t lt = lanemask_lt();
 
     const uint32_t nwarps = gridDim.x * PAIR_WARPS;
-    for (uint32_t grp = blockIdx.x * PAIR_WARPS + warp; grp < num_groups; grp += nwarps) {
+    for (uint32_t gi = blockIdx.x * PAIR_WARPS + warp; gi < num_groups; gi += nwarps) {
+        const uint32_t grp = p.glist ? p.glist[gi] : gi;
         const uint32_t row = grp / gx;
         const int ix = (int)(grp - row * gx);
         const int cz = (int)(row / gy), iy = (int)(row - (uint32_t)cz * gy);
@@ -993,7 +1034,7 @@ rg_fillmask_kernel(const PairParams<T>* __restrict__ params_dev, long long* __re
     const int nx = hp->nx, ny = hp->ny, nz = hp->nz, S = hp->group_cells, Sy = hp->group_cells_y, pad = hp->pad;
     const uint32_t gx = (uint32_t)hp->gx;
     const uint32_t gy = (uint32_t)((ny + Sy - 1) / Sy);
-    const uint32_t num_groups = (uint32_t)hp->num_groups;
+    const uint32_t num_groups = p.glist ? hp->active_groups : (uint32_t)hp->num_groups;
     const int Wd = 2 * pad + 1, Wy = Sy + 2 * pad, nrun = Wy * Wd;
     const int lane_dy = (lane % Wy) - pad, lane_dz = (lane / Wy) - pad;
     const uint32_t lt = lanemask_lt();
@@ -1001,8 +1042,9 @@ rg_fillmask_kernel(const PairParams<T>* __restrict__ params_dev, long long* __re
     // target ranges and source run of a group; the next group's are requested while the current group
     // is written, so that one round trip to memory per group (the candidate records) stays exposed
     struct GroupDesc { uint32_t tb0, te0, tb1, te1; int run_a, run_len; };
-    auto fetch = [&](uint32_t grp) -> GroupDesc {
+    auto fetch = [&](uint32_t gi) -> GroupDesc {
         GroupDesc d;
+        const uint32_t grp = p.glist ? p.glist[gi] : gi;
         const uint32_t row = grp / gx;
         const int ix = (int)(grp - row * gx);
         const int cz = (int)(row / gy), iy = (int)(row - (uint32_t)cz * gy);
@@ -1302,6 +1344,8 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
         PairParams<T> pp;
         pp.h = h; pp.cstart = ccount; pp.tcstart = tccount; pp.spos = spos; pp.scode = scode; pp.smeta = smeta; pp.hitmask = hitmask; pp.counts_out = counts_out; pp.tpos = tpos;
         pp.tmeta = tmeta; pp.tcount = tcount; pp.toffset = toffset; pp.r2 = (T)radius * (T)radius;
+        // the targets' fill counters are free once the targets are binned: they hold the list of groups with targets
+        pp.glist = (targets != nullptr) ? tcfill : nullptr;
         memcpy(init + RG_PARAMS_OFFSET, &pp, sizeof(pp));
     }
     // Small pageable source: cudaMemcpyAsync stages it before returning, so the stack buffer may die.
@@ -1339,6 +1383,8 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
     rg_bin_finalize_kernel<T><<<(unsigned)((nf + 255) / 256), 256, 0, stream>>>(
         N, Nt, targets, g, posw, aff, h, ccount, tccount, skey, scell, tkey, tcell, spos, scode, smeta, tpos, tmeta);
 
+    if (targets != nullptr)
+        rg_group_list_kernel<T><<<sm_count_cached() * 8, 256, 0, stream>>>(params_dev, tcfill);
     const int smem = PAIR_WARPS * PAIR_WARP_BYTES;
     DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_COUNT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int grid = sm_count_cached() * 4 * pair_grid_waves();

@@ -179,8 +179,10 @@ __device__ __forceinline__ void scan_apply_fused_body(const TIn* in, const uint3
                                                       const TOut* __restrict__ sums, int num_tiles, TOut* out, TOut* total_out)
 {
     __shared__ TOut warp_sums[SCAN_THREADS / 32];
-    const TOut before = scan_prefix_of_sums<TOut>(sums, num_tiles, total_out);
     const int64_t n = scan_count(n_dev, n_host);
+    // a tile past the (device-side) end has nothing to write; only the last block still adds up all sums for the total
+    if ((int64_t)blockIdx.x * SCAN_TILE >= n && (int)blockIdx.x != num_tiles - 1) return;
+    const TOut before = scan_prefix_of_sums<TOut>(sums, num_tiles, total_out);
     const int64_t base = (int64_t)blockIdx.x * SCAN_TILE + (int64_t)threadIdx.x * SCAN_ITEMS;
     TOut v[SCAN_ITEMS];
     TOut s = 0;

@@ -25,7 +25,10 @@ _STATE: dict = {}
 
 
 def _dev_state(device: torch.device) -> dict:
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    """Plan workspace and pinned header of one (device, stream): calls on different streams of a device get
+    workspaces of their own and so cannot race on one; calls on one stream are ordered by the stream."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (device.type, index, torch.cuda.current_stream(torch.device("cuda", index)).cuda_stream)
     st = _STATE.get(key)
     if st is None:
         pinned = torch.empty(64, dtype=torch.uint8).pin_memory()

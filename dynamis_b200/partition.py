@@ -31,8 +31,9 @@ _SCRATCH: dict = {}
 
 
 def scratch(device: torch.device, name: str, nbytes: int) -> torch.Tensor:
-    """Grow-only named device scratch buffers (uint8)."""
-    key = (device.index, name)
+    """Grow-only named device scratch buffers (uint8), one set per (device, stream): work on different streams of
+    a device never shares one."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream, name)
     buf = _SCRATCH.get(key)
     if buf is None or buf.numel() < nbytes:
         _SCRATCH.pop(key, None)
