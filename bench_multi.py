@@ -211,8 +211,10 @@ def run_exchange_parts(args, rank: int, world: int, dev: torch.device):
                 _lib.check(L.dynb_copy_async(r.remote_base + r.fwd_stage_off[0] + r.fwd_row_offset * rb,
                                              stage.data_ptr() + r.send_start * rb, r.send_count * rb, st), "copy_async")
 
-    res = {"push_only_ms": timed(lambda: begin(False, 0)), "copy_only_ms": timed(lambda: begin(True, 1)),
-           "push_and_copy_ms": timed(lambda: begin(True, 0)), "pack_ms": timed(pack), "peer_copies_ms": timed(peer_copies)}
+    res = {"push_only_ms": timed(lambda: begin(False, 0)), "push_only_in_list_order_ms": timed(lambda: begin(False, 2)),
+           "copy_only_ms": timed(lambda: begin(True, 1)), "push_and_copy_ms": timed(lambda: begin(True, 0)),
+           "push_and_copy_in_list_order_ms": timed(lambda: begin(True, 2)), "pack_ms": timed(pack),
+           "peer_copies_ms": timed(peer_copies)}
     e.check_status()
     if rank == 0:
         mb = n_send * rb / 1e6

@@ -264,15 +264,20 @@ __device__ __forceinline__ int find_seg(const PeerSeg* seg, int n, int64_t row)
 // Units [0, total) (V-wide pieces of the logical push list's rows) stored into the peers by `parts` blocks,
 // this block being `part`, interleaved like copy_span.  INDEXED: logical row i is x[index[i]] (forward),
 // else x[src_row_base + i] (ghost-gradient rows).
+// `stride` > 0: the block-sized pieces are visited in the order (k * stride) mod pieces (stride coprime to the
+// number of pieces, about 0.62 of it), so that at any moment the pieces in flight are spread over the whole
+// list — over all peers — instead of all ranks storing into the same peer's segment at the same time.
 template <typename V, bool INDEXED>
 __device__ void push_units(const dynb_halo_ctx& c, const V* __restrict__ x, int64_t n_rows_in, int64_t q,
                            const int64_t* __restrict__ index, int64_t src_row_base, const PeerSeg* seg, int nseg,
-                           int64_t total, int64_t part, int64_t parts)
+                           int64_t total, int64_t part, int64_t parts, unsigned long long stride)
 {
     constexpr int U = 4;
-    const int64_t bd = blockDim.x, step = parts * bd * U;
+    const int64_t bd = blockDim.x, piece = bd * U;
+    const unsigned long long pieces = (unsigned long long)((total + piece - 1) / piece);
     const bool small = total < (1ll << 32);
-    for (int64_t base = part * bd * U + threadIdx.x; base < total; base += step) {
+    for (unsigned long long k = (unsigned long long)part; k < pieces; k += (unsigned long long)parts) {
+        const int64_t base = (int64_t)(stride ? (k * stride) % pieces : k) * piece + threadIdx.x;
         V v[U];
         V* d[U];
 #pragma unroll
@@ -293,6 +298,20 @@ __device__ void push_units(const dynb_halo_ctx& c, const V* __restrict__ x, int6
 #pragma unroll
         for (int u = 0; u < U; u++)
             if (d[u] != nullptr) *d[u] = v[u];
+    }
+}
+
+// stride for push_units: an odd number near 0.618 * pieces that shares no factor with it (0 for short lists)
+__device__ unsigned long long scatter_stride(int64_t total, int64_t piece)
+{
+    const unsigned long long pieces = (unsigned long long)((total + piece - 1) / piece);
+    if (pieces < 64) return 0ull;
+    unsigned long long s = (unsigned long long)((double)pieces * 0.6180339887) | 1ull;
+    for (;;) {
+        unsigned long long a = s, b = pieces;
+        while (b) { const unsigned long long t = a % b; a = b; b = t; }
+        if (a == 1ull) return s;
+        s += 2ull;
     }
 }
 
@@ -322,7 +341,8 @@ halo_forward_begin_kernel(dynb_halo_ctx c, const V* __restrict__ x, int64_t n_lo
     }
     __syncthreads();
     const int64_t G = gridDim.x, b = blockIdx.x;
-    const int64_t P = skip_push ? 0 : total_send * q;
+    const int64_t P = (skip_push & 1) ? 0 : total_send * q;
+    const unsigned long long stride = (skip_push & 2) ? 0ull : scatter_stride(P, (int64_t)blockDim.x * 4);
     const unsigned char* xs = reinterpret_cast<const unsigned char*>(x);
     const int64_t head_bytes = n_local * row_bytes;
     // Even blocks push first and copy second, odd blocks the other way round: measured on four GPUs (2 M rows
@@ -330,9 +350,9 @@ halo_forward_begin_kernel(dynb_halo_ctx c, const V* __restrict__ x, int64_t n_lo
     // alone; alternating the two inside every warp gave 0.58 ms, blocks with a fixed role 0.54-0.87 ms.
     if (b & 1) {
         if (out_head != nullptr) copy_span(out_head, xs, head_bytes, head_vb, b, G);
-        push_units<V, true>(c, x, n_local, q, send_local, 0, seg, c.world_size, P, b, G);
+        push_units<V, true>(c, x, n_local, q, send_local, 0, seg, c.world_size, P, b, G, stride);
     } else {
-        push_units<V, true>(c, x, n_local, q, send_local, 0, seg, c.world_size, P, b, G);
+        push_units<V, true>(c, x, n_local, q, send_local, 0, seg, c.world_size, P, b, G, stride);
         if (out_head != nullptr) copy_span(out_head, xs, head_bytes, head_vb, b, G);
     }
     last_block_signals(c, 0, gen, announce);
@@ -372,6 +392,7 @@ halo_backward_begin_kernel(dynb_halo_ctx c, const V* __restrict__ g, int64_t n_l
     __syncthreads();
     const int64_t G = gridDim.x, b = blockIdx.x;
     const int64_t P = n_ghost * q;
+    const unsigned long long stride = scatter_stride(P, (int64_t)blockDim.x * 4);
     const unsigned char* gs = reinterpret_cast<const unsigned char*>(g);
     const int64_t own_bytes = n_local * row_bytes;
     // has_recv comes only with 16-byte aligned rows of at least 64 bytes (host side): rows that the second half
@@ -379,9 +400,9 @@ halo_backward_begin_kernel(dynb_halo_ctx c, const V* __restrict__ g, int64_t n_l
     if (b & 1) {
         if (has_recv == nullptr) copy_span(out, gs, own_bytes, out_vb, b, G);
         else copy_rows_unflagged(reinterpret_cast<uint4*>(out), reinterpret_cast<const uint4*>(g), has_recv, n_local, row_bytes >> 4, b, G);
-        push_units<V, false>(c, g, n_local + n_ghost, q, nullptr, n_local, seg, c.world_size, P, b, G);
+        push_units<V, false>(c, g, n_local + n_ghost, q, nullptr, n_local, seg, c.world_size, P, b, G, stride);
     } else {
-        push_units<V, false>(c, g, n_local + n_ghost, q, nullptr, n_local, seg, c.world_size, P, b, G);
+        push_units<V, false>(c, g, n_local + n_ghost, q, nullptr, n_local, seg, c.world_size, P, b, G, stride);
         if (has_recv == nullptr) copy_span(out, gs, own_bytes, out_vb, b, G);
         else copy_rows_unflagged(reinterpret_cast<uint4*>(out), reinterpret_cast<const uint4*>(g), has_recv, n_local, row_bytes >> 4, b, G);
     }

@@ -270,11 +270,13 @@ typedef struct dynb_halo_ctx {
 /* Forward, first half (one launch): send-list rows -> peers' ghost regions; x[0:n_local] -> out_head
  * (NULL: no local copy); then the generation signal, carrying announce_slot (0 = "store my next ghost
  * rows into my staging buffer", s + 1 = "into my result slot s") and the drift word.  The destination of
- * this generation's rows is what each peer announced with its previous signal.  skip_push != 0: the rows
- * were delivered by other means (copy engine) before this call; only copy and signal. */
+ * this generation's rows is what each peer announced with its previous signal.  flags bit 0: the rows
+ * were delivered by other means (copy engine) before this call; only copy and signal.  flags bit 1: walk
+ * the send list front to back; by default its block-sized pieces are visited in a scattered order, so that
+ * the ranks do not all store into the same peer's segment at the same time. */
 int dynb_halo_forward_begin(const dynb_halo_ctx* ctx, const void* x_dev, int64_t n_local, int64_t row_bytes,
                             const int64_t* send_local_dev, int64_t total_send, void* out_head_dev, uint32_t gen,
-                            uint32_t announce_slot, int skip_push, void* stream);
+                            uint32_t announce_slot, int flags, void* stream);
 /* Forward, second half (one launch): waits at most timeout_ns for every peer's signal of `gen`, ORs the
  * drift words into drift_global, and copies stage_dev -> out_tail_dev when the rows arrived in staging
  * (out_tail_dev NULL: they are already in place).  On expiry the status words are set and the kernel
