@@ -63,6 +63,7 @@ struct DevHeader {
     double clip_lo[3];  // source images outside [clip_lo, clip_hi] cannot reach any target and are dropped
     double clip_hi[3];
     uint32_t active_groups;  // entries of the list of groups that hold targets (target subsets only)
+    uint32_t long_groups;    // entries of the list of groups whose candidate list is too long for the hit bits
 };
 static_assert(offsetof(DevHeader, ncell_plus1) == sizeof(dynb_rg_header), "public header prefix mismatch");
 
@@ -675,6 +676,7 @@ template <typename T> struct PairParams {
     const uint2* smeta;       // [M] {atom id, packed shift code} per source record
     int32_t* counts_out;      // [Nt] degrees in caller order, or nullptr
     const uint32_t* glist;    // groups that hold at least one target (h->active_groups entries), or nullptr = all groups
+    uint32_t* long_list;      // groups whose candidate list exceeds the hit bits (h->long_groups entries, written by COUNT)
     T r2;
 };
 // The plan stores its PairParams inside the workspace (after the header) so that the fill call
@@ -740,12 +742,15 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
 
     DevHeader* hp = p.h;
     if (hp->status & RG_FATAL) return;
-    if (MODE == MODE_FILL && skip_if_masks && hp->reserved[0] <= RG_MASK_SLOTS) return;  // rg_fillmask_kernel does it
+    // behind rg_fillmask_kernel this pass writes only the groups whose candidate list was too long for the hit bits
+    const bool long_only = (MODE == MODE_FILL) && skip_if_masks;
+    if (long_only && hp->long_groups == 0u) return;
     int warp_max_slots = 0, warp_max_degree = 0;
     const int nx = hp->nx, ny = hp->ny, nz = hp->nz, S = hp->group_cells, Sy = hp->group_cells_y, pad = hp->pad;
     const uint32_t gx = (uint32_t)hp->gx;
     const uint32_t gy = (uint32_t)((ny + Sy - 1) / Sy);
-    const uint32_t num_groups = p.glist ? hp->active_groups : (uint32_t)hp->num_groups;  // < 2^31: never more groups than cells
+    const uint32_t num_groups = long_only ? hp->long_groups
+                                          : (p.glist ? hp->active_groups : (uint32_t)hp->num_groups);  // < 2^31: never more groups than cells
     const int Wd = 2 * pad + 1, Wy = Sy + 2 * pad, nrun = Wy * Wd;
     const int lane_dy = (lane % Wy) - pad, lane_dz = (lane / Wy) - pad;
     const T r2 = p.r2;
@@ -754,7 +759,7 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
 
     const uint32_t nwarps = gridDim.x * PAIR_WARPS;
     for (uint32_t gi = blockIdx.x * PAIR_WARPS + warp; gi < num_groups; gi += nwarps) {
-        const uint32_t grp = p.glist ? p.glist[gi] : gi;
+        const uint32_t grp = long_only ? p.long_list[gi] : (p.glist ? p.glist[gi] : gi);
         const uint32_t row = grp / gx;
         const int ix = (int)(grp - row * gx);
         const int cz = (int)(row / gy), iy = (int)(row - (uint32_t)cz * gy);
@@ -790,6 +795,7 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
         runs_compact(delta, run_a, run_off, run_len, lt);
         const bool write_masks = (MODE == MODE_COUNT) && nslots_total <= RG_MASK_SLOTS;
         warp_max_slots = max(warp_max_slots, nslots_total);
+        if (MODE == MODE_COUNT && nslots_total > RG_MASK_SLOTS && lane == 0) p.long_list[atomicAdd(&hp->long_groups, 1u)] = grp;
 
         for (int cbeg = 0, chunk = 0; cbeg < L; cbeg += CAP, chunk++) {
             const int clen = min(CAP, L - cbeg);
@@ -1030,7 +1036,6 @@ rg_fillmask_kernel(const PairParams<T>* __restrict__ params_dev, long long* __re
 
     const DevHeader* hp = p.h;
     if (hp->status & RG_FATAL) return;
-    if (hp->reserved[0] > RG_MASK_SLOTS) return;  // masks incomplete: rg_pair_kernel<FILL> writes the edges
     const int nx = hp->nx, ny = hp->ny, nz = hp->nz, S = hp->group_cells, Sy = hp->group_cells_y, pad = hp->pad;
     const uint32_t gx = (uint32_t)hp->gx;
     const uint32_t gy = (uint32_t)((ny + Sy - 1) / Sy);
@@ -1092,8 +1097,8 @@ rg_fillmask_kernel(const PairParams<T>* __restrict__ params_dev, long long* __re
         }
         int L;
         const int run_off = warp_excl_scan(run_len, lane, &L);
-        const int nslots = min((L + 31) >> 5, RG_MASK_SLOTS);
-        if (nslots == 0) continue;
+        const int nslots = (L + 31) >> 5;
+        if (nslots == 0 || nslots > RG_MASK_SLOTS) continue;  // a longer list has no hit bits: rg_pair_kernel<FILL> writes that group
 
         __syncwarp();
         runs_compact(delta, run_a, run_off, run_len, lt);
@@ -1346,6 +1351,7 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
         pp.tmeta = tmeta; pp.tcount = tcount; pp.toffset = toffset; pp.r2 = (T)radius * (T)radius;
         // the targets' fill counters are free once the targets are binned: they hold the list of groups with targets
         pp.glist = (targets != nullptr) ? tcfill : nullptr;
+        pp.long_list = cfill;   // likewise free once the sources are binned
         memcpy(init + RG_PARAMS_OFFSET, &pp, sizeof(pp));
     }
     // Small pageable source: cudaMemcpyAsync stages it before returning, so the stack buffer may die.
@@ -1407,9 +1413,9 @@ static int rg_fill(const void* ws, int64_t* ei, float* shifts, void* d2out, int6
     const int grid = sm_count_cached() * 4 * pair_grid_waves();
     GlueArgs glue{};
     if (glue_opt != nullptr) glue = *glue_opt;
-    // Without distances the edges can come from the hit masks of the counting pass; which of the two
-    // kernels does the work is decided on the device (header word written by the counting pass), the
-    // other one returns at once.
+    // Without distances the edges come from the hit masks of the counting pass; the groups whose candidate
+    // list was too long for the masks (listed on the device by the counting pass; usually none) are written
+    // by the distance-recomputing pass behind it.
     const int use_masks = (d2out == nullptr) ? 1 : 0;
     if (use_masks) {
         const int fsmem = PAIR_WARPS * FM_WARP_BYTES;
@@ -1421,7 +1427,7 @@ static int rg_fill(const void* ws, int64_t* ei, float* shifts, void* d2out, int6
             rg_fillmask_kernel<T, false><<<grid, PAIR_THREADS, fsmem, stream>>>(params_dev, reinterpret_cast<long long*>(ei), shifts, (long long)E, glue);
         }
     }
-    // behind the bit-driven writer this launch is idle in all but unusual inputs: two waves keep its cost low
+    // behind the bit-driven writer this launch only has the listed long groups to do (usually none): two waves keep its cost low
     const int fgrid = use_masks ? sm_count_cached() * 4 * std::min(2, pair_grid_waves()) : grid;
     rg_pair_kernel<T, MODE_FILL><<<fgrid, PAIR_THREADS, smem, stream>>>(
         params_dev, reinterpret_cast<long long*>(ei), shifts, static_cast<T*>(d2out), (long long)E, HaloArgs{}, use_masks, glue);

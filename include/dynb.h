@@ -62,8 +62,8 @@ typedef struct dynb_rg_header {
     int32_t grid[3];    /* cell grid dimensions chosen on the device */
     int32_t group_cells;/* cells per warp work item along x */
     int64_t num_groups;
-    int64_t reserved[2]; /* [0]: 0, or the longest candidate list in 32-record slots when it exceeded the 16 slots the
-                          * count pass keeps hit bits for (dynb_rg_fill then recomputes the distances); [1]: unused */
+    int64_t reserved[2]; /* [0]: 0, or the longest candidate list in 32-record slots when one exceeded the 16 slots the
+                          * count pass keeps hit bits for (dynb_rg_fill recomputes the distances of those groups); [1]: unused */
 } dynb_rg_header;
 
 /* Suggested capacities for a system: src_capacity bounds the number of periodic images

@@ -153,6 +153,44 @@ def test_target_subset_unsorted_with_duplicates(cuda):
     _check_vs_oracle(pos, cell, pbc, 5.0, cuda, targets=targets, what="subset")
 
 
+@pytest.mark.parametrize("case", ["x", "xyz", "thin_gap", "pbc_xy", "triclinic", "unwrapped"])
+def test_target_subset_touching_the_periodic_boundary(cuda, case):
+    """A rank's atoms form a compact subdomain that wraps around the periodic boundary: after the wrap the
+    targets sit at both ends of the box and the grid spans it, with the cell scan walking only the groups that hold
+    targets; the edges must be the oracle's in every case."""
+    rng = np.random.default_rng(606)
+    n, L, r = 20000, 80.0, 5.0
+    cell = (np.eye(3) * L).astype(np.float32)
+    pbc = [True, True, True]
+    pos = (rng.random((n, 3)) * L).astype(np.float32)
+
+    def arc(c, lo, hi):     # coordinates in [lo, L) or [0, hi)
+        return (c >= lo) | (c < hi)
+
+    if case == "x":
+        sel = arc(pos[:, 0], 70.0, 18.0)
+    elif case == "xyz":
+        sel = arc(pos[:, 0], 66.0, 12.0) & arc(pos[:, 1], 75.0, 20.0) & arc(pos[:, 2], 60.0, 5.0)
+    elif case == "thin_gap":   # the empty stretch is shorter than twice the reach: no shifted frame, still right
+        sel = arc(pos[:, 0], 12.0, 4.0)
+    elif case == "pbc_xy":
+        pbc = [True, True, False]
+        sel = arc(pos[:, 0], 70.0, 18.0) & arc(pos[:, 2], 0.0, 30.0)
+    elif case == "triclinic":
+        cell = np.array([[L, 0, 0], [0.2 * L, L, 0], [0.1 * L, 0, L]], dtype=np.float32)
+        pos = (rng.random((n, 3)) @ cell.astype(np.float64)).astype(np.float32)
+        sel = arc(pos[:, 0], 70.0, 18.0)
+    else:                      # targets given outside the cell: x in [-10, 18) wraps to [70, 80) and [0, 18)
+        pos[:, 0] = pos[:, 0] - 10.0
+        sel = pos[:, 0] < 18.0
+    targets = np.nonzero(sel)[0].astype(np.int64)
+    assert 100 < targets.size < n
+    _check_vs_oracle(pos, cell, pbc, r, cuda, targets=targets, what=case)
+    # the owned atoms first, as a rank holds them ([owned | halo] with targets 0..n_own-1)
+    order = np.concatenate([targets, np.nonzero(~sel)[0]])
+    _check_vs_oracle(pos[order], cell, pbc, r, cuda, targets=np.arange(targets.size, dtype=np.int64), what=case + "/owned first")
+
+
 def test_counts_only_matches(cuda):
     import dynamis_b200 as D
 
