@@ -412,65 +412,76 @@ halo_backward_begin_kernel(dynb_halo_ctx c, const V* __restrict__ g, int64_t n_l
 // Reverse, second half: bounded wait, drift OR, then for every owned row named by the send list
 // out[row] = g[row] + the received rows that name it, in the fixed order of inv_entries.
 template <typename T, typename V, int VW>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 halo_backward_end_kernel(dynb_halo_ctx c, uint32_t gen, unsigned long long budget_ns, const V* __restrict__ g,
                          const int64_t* __restrict__ rows, const uint32_t* __restrict__ row_first, int64_t n_rows, int64_t q,
                          const V* __restrict__ recv, const int64_t* __restrict__ inv_offsets,
                          const uint32_t* __restrict__ inv_entries, V* __restrict__ out)
 {
-    wait_all(c, 1, gen, budget_ns);
-    if (blockIdx.x == 0) drift_or(c, 1, gen);
-    // one warp per listed row, R rows in flight; lanes walk the row's V-wide columns
+    // one warp per listed row, R rows in flight; lanes walk the row's V-wide columns.  What does not depend on
+    // the peers — the rows' ids and their places in the inverse CSR — is requested before the wait for the warp's
+    // first step, so that behind the wait the gradient rows and the received rows are one round of independent loads.
     constexpr int R = 4;
     const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
     const int64_t nw = (int64_t)gridDim.x * wpb, w = (int64_t)blockIdx.x * wpb + (threadIdx.x >> 5);
-    for (int64_t r0 = w * R; r0 < n_rows; r0 += nw * R) {
-        // row_first (optional): the first received row of every listed row, so that the row, its first received
-        // row and (below) both rows' data are two rounds of independent loads instead of four dependent ones
-        int64_t row[R], b[R], e[R];
-        uint32_t first[R];
+    struct Step { int64_t row[R]; uint32_t b[R], e[R], first[R]; };   // list places fit 32 bits (dynb_inverse_csr)
+    auto request = [&](int64_t r0, Step& s) {
 #pragma unroll
         for (int k = 0; k < R; k++) {
-            row[k] = -1;
-            first[k] = 0;
+            s.row[k] = -1;
+            s.first[k] = 0;
             if (r0 + k < n_rows) {
-                row[k] = rows[r0 + k];
-                if (row_first != nullptr) first[k] = row_first[r0 + k];
+                s.row[k] = rows[r0 + k];
+                if (row_first != nullptr) s.first[k] = row_first[r0 + k];
             }
         }
 #pragma unroll
-        for (int k = 0; k < R; k++)
-            if (row[k] >= 0) { b[k] = inv_offsets[row[k]]; e[k] = inv_offsets[row[k] + 1]; }
+        for (int k = 0; k < R; k++) {
+            s.b[k] = s.e[k] = 0;
+            if (s.row[k] >= 0) {
+                s.b[k] = (uint32_t)inv_offsets[s.row[k]];
+                s.e[k] = (uint32_t)inv_offsets[s.row[k] + 1];
+            }
+        }
+    };
+    Step cur;
+    int64_t r0 = w * R;
+    if (r0 < n_rows) request(r0, cur);
+    wait_all(c, 1, gen, budget_ns);
+    if (blockIdx.x == 0) drift_or(c, 1, gen);
+    while (r0 < n_rows) {
         for (int64_t col = lane; col < q; col += 32) {
             V v[R], f[R];
             bool hf[R];
 #pragma unroll
             for (int k = 0; k < R; k++) {
                 hf[k] = false;
-                if (row[k] >= 0) {
-                    v[k] = g[row[k] * q + col];
-                    hf[k] = b[k] < e[k];
-                    if (hf[k]) f[k] = recv[(int64_t)(row_first != nullptr ? first[k] : inv_entries[b[k]]) * q + col];
+                if (cur.row[k] >= 0) {
+                    v[k] = g[cur.row[k] * q + col];
+                    hf[k] = cur.b[k] < cur.e[k];
+                    if (hf[k]) f[k] = recv[(int64_t)(row_first != nullptr ? cur.first[k] : inv_entries[cur.b[k]]) * q + col];
                 }
             }
 #pragma unroll
             for (int k = 0; k < R; k++) {
-                if (row[k] < 0) continue;
+                if (cur.row[k] < 0) continue;
                 T* a = reinterpret_cast<T*>(&v[k]);
                 if (hf[k]) {
                     const T* fr = reinterpret_cast<const T*>(&f[k]);
 #pragma unroll
                     for (int cc = 0; cc < VW; cc++) a[cc] += fr[cc];
                 }
-                for (int64_t j = b[k] + 1; j < e[k]; j++) {
+                for (uint32_t j = cur.b[k] + 1; j < cur.e[k]; j++) {
                     const V xx = recv[(int64_t)inv_entries[j] * q + col];
                     const T* xr = reinterpret_cast<const T*>(&xx);
 #pragma unroll
                     for (int cc = 0; cc < VW; cc++) a[cc] += xr[cc];
                 }
-                out[row[k] * q + col] = v[k];
+                out[cur.row[k] * q + col] = v[k];
             }
         }
+        r0 += nw * R;
+        if (r0 < n_rows) request(r0, cur);
     }
 }
 
