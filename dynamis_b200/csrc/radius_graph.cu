@@ -132,6 +132,37 @@ __device__ __forceinline__ uint32_t cell_of(const DevHeader& h, T x, T y, T z)
 // ------------------------------------------------------------------------------------------
 // rg_wrap
 // ------------------------------------------------------------------------------------------
+// Squared distance with the rounding every pass must share (the contraction nvcc applies to
+// dx*dx + dy*dy + dz*dz, written out so that no pass depends on the compiler's choice):
+// fma(dz, dz, fma(dx, dx, dy * dy)).
+template <typename T> __device__ __forceinline__ T dist2(T ax, T ay, T az, T sx, T sy, T sz)
+{
+    const T dx = sub_rn(ax, sx), dy = sub_rn(ay, sy), dz = sub_rn(az, sz);
+    return fma_rn(dz, dz, fma_rn(dx, dx, mul_rn(dy, dy)));
+}
+// The same for two fp32 candidates at once with the packed fp32 instructions of sm_100 (each half is an
+// IEEE round-to-nearest operation, so the halves equal dist2<float> bit for bit); one instruction issue
+// per two tests.
+__device__ __forceinline__ unsigned long long f32x2_pack(float lo, float hi)
+{
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void dist2_x2(unsigned long long ax2, unsigned long long ay2, unsigned long long az2,
+                                         unsigned long long sx2, unsigned long long sy2, unsigned long long sz2,
+                                         float& d_lo, float& d_hi)
+{
+    unsigned long long dx, dy, dz, d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(dx) : "l"(ax2), "l"(sx2));
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(dy) : "l"(ay2), "l"(sy2));
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(dz) : "l"(az2), "l"(sz2));
+    asm("mul.rn.f32x2 %0, %1, %1;" : "=l"(d) : "l"(dy));
+    asm("fma.rn.f32x2 %0, %1, %1, %2;" : "=l"(d) : "l"(dx), "l"(d));
+    asm("fma.rn.f32x2 %0, %1, %1, %2;" : "=l"(d) : "l"(dz), "l"(d));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d_lo), "=f"(d_hi) : "l"(d));
+}
+
 constexpr int WRAP_THREADS = 256;
 
 template <typename T>
@@ -522,7 +553,7 @@ rg_bin_finalize_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ target
                        DevHeader* __restrict__ hp, const uint32_t* __restrict__ cstart,
                        const uint32_t* __restrict__ tcstart, const unsigned long long* __restrict__ skey,
                        const uint32_t* __restrict__ scell, const uint32_t* __restrict__ tkey,
-                       const uint32_t* __restrict__ tcell, Vec4<T>* __restrict__ spos,
+                       const uint32_t* __restrict__ tcell, Vec4<T>* __restrict__ spos, float* __restrict__ sxyz, long long sxyz_stride,
                        uint32_t* __restrict__ scode, uint2* __restrict__ smeta, Vec4<T>* __restrict__ tpos, int4* __restrict__ tmeta)
 {
     const DevHeader h = *hp;
@@ -547,6 +578,11 @@ rg_bin_finalize_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ target
         image_pos(g, w.x, w.y, w.z, dx, dy, dz, r.x, r.y, r.z);
         r.w = bits_to_real((int32_t)atom, T());
         spos[b + rank] = r;
+        if (sizeof(T) == 4 && sxyz != nullptr) {
+            sxyz[b + rank] = (float)r.x;
+            sxyz[sxyz_stride + b + rank] = (float)r.y;
+            sxyz[2 * sxyz_stride + b + rank] = (float)r.z;
+        }
         const int ex = dx - ff.x, ey = dy - ff.y, ez = dz - ff.z;
         if (ex < -511 || ex > 511 || ey < -511 || ey > 511 || ez < -511 || ez > 511) {
             atomicOr(&hp->status, DYNB_RG_SHIFT_RANGE);
@@ -634,7 +670,7 @@ struct HaloArgs {
 };
 
 #ifndef DYNB_COUNT_UNROLL
-#define DYNB_COUNT_UNROLL 2
+#define DYNB_COUNT_UNROLL 1
 #endif
 constexpr int COUNT_UNROLL = DYNB_COUNT_UNROLL;  // unroll factor of the count pass's test loop (tuning knob at build time)
 constexpr int RG_MASK_SLOTS = 16;  // hit bits kept per lane and target (candidate lists up to 512 records)
@@ -667,6 +703,8 @@ template <typename T> struct PairParams {
     const uint32_t* cstart;
     const uint32_t* tcstart;
     const Vec4<T>* spos;
+    const float* sxyz;        // fp32 only: coordinates of the source records as three arrays, each sxyz_stride long
+    long long sxyz_stride;
     const uint32_t* scode;    // packed (shift - floor(frac) of the source atom), 10 bits per axis, bias 512
     const Vec4<T>* tpos;
     const int4* tmeta;
@@ -722,17 +760,30 @@ rg_group_list_kernel(const PairParams<T>* __restrict__ params_dev, uint32_t* __r
     }
 }
 
-template <typename T, int MODE>
+template <typename T, int MODE, bool BYVAL>
 __global__ void __launch_bounds__(PAIR_THREADS, 4)
-rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restrict__ ei, float* __restrict__ shifts,
-               T* __restrict__ d2out, const long long E, const HaloArgs halo, const int skip_if_masks, const GlueArgs glue)
+rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, const PairParams<T> params_val, long long* __restrict__ ei,
+               float* __restrict__ shifts, T* __restrict__ d2out, const long long E, const HaloArgs halo, const int skip_if_masks,
+               const GlueArgs glue)
 {
-    const PairParams<T> p = *params_dev;
+    // BYVAL: the launch has the record at hand and passes it as a kernel argument; its fields are then operands
+    // of the instructions instead of registers loaded (and, under register pressure, reloaded) from the workspace
+    PairParams<T> params_loaded;
+    if constexpr (!BYVAL) params_loaded = *params_dev;
+    const PairParams<T>& p = BYVAL ? params_val : params_loaded;
     extern __shared__ __align__(32) unsigned char smem_raw[];
     constexpr int CAP = PAIR_CAND_BYTES / (int)sizeof(Vec4<T>);
+    // The fp32 count pass keeps its candidates as three arrays of coordinates (no atom ids, no shift codes: the
+    // space of both holds a whole list with hit bits) laid out for the packed distance test: the 8 bytes that
+    // lane l reads for block b hold the coordinate of candidates 64 b + l and 64 b + 32 + l.
+    constexpr bool PACKED = (MODE == MODE_COUNT) && sizeof(T) == 4;
+    constexpr int PK = RG_MASK_SLOTS * 32;
+    constexpr int CAPX = PACKED ? PK : CAP;
+    static_assert(3 * 4 * PK <= PAIR_CAND_BYTES + PAIR_CODE_BYTES, "packed candidates must fit the record and code space");
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     unsigned char* wbase = smem_raw + warp * PAIR_WARP_BYTES;
     Vec4<T>* cand = reinterpret_cast<Vec4<T>*>(wbase);
+    float* xs = reinterpret_cast<float*>(wbase);
     uint32_t* codes = reinterpret_cast<uint32_t*>(wbase + PAIR_CAND_BYTES);
     unsigned short* listA = reinterpret_cast<unsigned short*>(wbase + PAIR_CAND_BYTES + PAIR_CODE_BYTES);
     unsigned short* listB = listA + PAIR_LIST;
@@ -797,13 +848,38 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
         warp_max_slots = max(warp_max_slots, nslots_total);
         if (MODE == MODE_COUNT && nslots_total > RG_MASK_SLOTS && lane == 0) p.long_list[atomicAdd(&hp->long_groups, 1u)] = grp;
 
-        for (int cbeg = 0, chunk = 0; cbeg < L; cbeg += CAP, chunk++) {
-            const int clen = min(CAP, L - cbeg);
+        for (int cbeg = 0, chunk = 0; cbeg < L; cbeg += CAPX, chunk++) {
+            const int clen = min(CAPX, L - cbeg);
             const int clen32 = (clen + 31) & ~31;
-            const bool more_chunks = cbeg + CAP < L;
+            const bool more_chunks = cbeg + CAPX < L;
             // dense staging: slot j of the list holds flattened candidate cbeg + j; all loads of a chunk are
             // independent
             int rank_base = runs_flags(flags, run_off, run_len, lane, cbeg);
+            if constexpr (PACKED) {
+                // Per 64 candidates two rounds; in each the lower half-warp takes 16 candidates of the block's
+                // first 32 and the upper half-warp 16 of its second 32, so that the 32 four-byte stores of a
+                // round fall into 32 different banks and each half-warp reads 64 contiguous bytes per array.
+                const int half = lane >> 4, l16 = lane & 15;
+                for (int blk = 0; blk * 64 < clen; blk++) {
+                    const uint32_t w0 = flags[2 * blk], w1 = flags[2 * blk + 1];
+                    const uint32_t word = half ? w1 : w0;
+                    const int base = rank_base + (half ? __popc(w0) : 0);
+                    rank_base += __popc(w0) + __popc(w1);
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        const int bitpos = i * 16 + l16;
+                        const int j = blk * 64 + half * 32 + bitpos;
+                        if (j < clen) {
+                            const int r = base + __popc(word & ((2u << bitpos) - 1u)) - 1;
+                            const float* src = p.sxyz + (delta[r] + cbeg + j);
+                            float* dst = &xs[blk * 64 + bitpos * 2 + half];
+                            cp_async<4>(dst, src);
+                            cp_async<4>(dst + PK, src + p.sxyz_stride);
+                            cp_async<4>(dst + 2 * PK, src + 2 * p.sxyz_stride);
+                        }
+                    }
+                }
+            } else {
             for (int j = lane, sw = 0; j < clen32; j += 32, sw++) {
                 const uint32_t word = flags[sw];
                 const int r = rank_base + __popc(word & le) - 1;
@@ -819,7 +895,11 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                     if (MODE == MODE_FILL) cp_async<4>(&codes[j], &p.scode[gidx]);
                 }
             }
-            if (clen + lane < clen32) {
+            }
+            if constexpr (PACKED) {
+                // x alone keeps a padding slot out of every cutoff (its distance is infinite or not a number)
+                for (int j = clen + lane; j < ((clen + 63) & ~63); j += 32) xs[(j >> 6) * 64 + (j & 31) * 2 + ((j >> 5) & 1)] = 3.0e38f;
+            } else if (clen + lane < clen32) {
                 Vec4<T> c;
                 c.x = c.y = c.z = (T)3.0e38f;  // never within the cutoff
                 c.w = (T)0;
@@ -828,6 +908,100 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
             cp_async_wait_all();
             __syncwarp();
 
+          if constexpr (MODE == MODE_COUNT) {
+            // the targets of both rows of the group as one list, two targets per candidate load
+            const uint32_t n0 = te[0] - tb[0], ntot = n0 + (te[1] - tb[1]);
+            for (uint32_t k = 0; k < ntot; k += 2) {
+                const bool has2 = (k + 1 < ntot);
+                const uint32_t kb = has2 ? k + 1 : k;
+                const uint32_t tA = (k < n0) ? tb[0] + k : tb[1] + (k - n0);
+                const uint32_t tB = (kb < n0) ? tb[0] + kb : tb[1] + (kb - n0);
+                const Vec4<T> tpA = p.tpos[tA];
+                const Vec4<T> tpB = p.tpos[tB];
+                const T ax = tpA.x, ay = tpA.y, az = tpA.z, bx = tpB.x, by = tpB.y, bz = tpB.z;
+                // lane l keeps, for each of its candidates l, 32 + l, 64 + l, ..., one hit bit per target; the
+                // bits are stored so that the edge-writing pass need not repeat the distance tests.  A list too
+                // long for the bits is only counted.
+                unsigned short* mrowA = p.hitmask + (size_t)tA * 32;
+                unsigned short* mrowB = p.hitmask + (size_t)tB * 32;
+                uint32_t bitsA = 0, bitsB = 0;
+                int ca = 0, cb = 0;
+                if (chunk != 0) {
+                    if (write_masks) {
+                        bitsA = mrowA[lane];
+                        bitsB = mrowB[lane];
+                    } else {
+                        ca = (int)p.tcount[tA];
+                        cb = has2 ? (int)p.tcount[tB] : 0;
+                    }
+                }
+                uint32_t bit = 1u << (cbeg >> 5);
+                if constexpr (PACKED) {
+                    const unsigned long long ax2 = f32x2_pack(ax, ax), ay2 = f32x2_pack(ay, ay), az2 = f32x2_pack(az, az);
+                    const unsigned long long bx2 = f32x2_pack(bx, bx), by2 = f32x2_pack(by, by), bz2 = f32x2_pack(bz, bz);
+                    const unsigned long long* x2 = reinterpret_cast<const unsigned long long*>(xs) + lane;
+                    const int nblk = (clen + 63) >> 6;
+                    int na = 0, nb = 0;
+#pragma unroll COUNT_UNROLL
+                    for (int blk = 0; blk < nblk; blk++) {
+                        const unsigned long long sx2 = x2[blk * 32], sy2 = x2[PK / 2 + blk * 32], sz2 = x2[PK + blk * 32];
+                        float a0, a1, b0, b1;
+                        dist2_x2(ax2, ay2, az2, sx2, sy2, sz2, a0, a1);
+                        dist2_x2(bx2, by2, bz2, sx2, sy2, sz2, b0, b1);
+                        const bool ha0 = (a0 <= r2) && (a0 > eps), ha1 = (a1 <= r2) && (a1 > eps);
+                        const bool hb0 = (b0 <= r2) && (b0 > eps), hb1 = (b1 <= r2) && (b1 > eps);
+                        if (write_masks) {
+                            bitsA |= (ha0 ? bit : 0u) | (ha1 ? (bit << 1) : 0u);
+                            bitsB |= (hb0 ? bit : 0u) | (hb1 ? (bit << 1) : 0u);
+                            bit <<= 2;
+                        } else {
+                            na += (ha0 ? 1 : 0) + (ha1 ? 1 : 0);
+                            nb += (hb0 ? 1 : 0) + (hb1 ? 1 : 0);
+                        }
+                    }
+                    if (!write_masks) {
+                        ca += __reduce_add_sync(0xffffffffu, na);
+                        cb += __reduce_add_sync(0xffffffffu, nb);
+                    }
+                } else {
+                    int na = 0, nb = 0;
+#pragma unroll COUNT_UNROLL
+                    for (int kk = 0; kk < clen32; kk += 32) {
+                        const Vec4<T> c = cand[kk + lane];
+                        const T dA = dist2<T>(ax, ay, az, c.x, c.y, c.z);
+                        const T dB = dist2<T>(bx, by, bz, c.x, c.y, c.z);
+                        const bool hA = (dA <= r2) && (dA > eps), hB = (dB <= r2) && (dB > eps);
+                        if (write_masks) {
+                            bitsA |= hA ? bit : 0u;
+                            bitsB |= hB ? bit : 0u;
+                            bit <<= 1;
+                        } else {
+                            na += hA ? 1 : 0;
+                            nb += hB ? 1 : 0;
+                        }
+                    }
+                    if (!write_masks) {
+                        ca += __reduce_add_sync(0xffffffffu, na);
+                        cb += __reduce_add_sync(0xffffffffu, nb);
+                    }
+                }
+                if (write_masks) {
+                    mrowA[lane] = (unsigned short)bitsA;
+                    if (has2) mrowB[lane] = (unsigned short)bitsB;
+                    ca = __reduce_add_sync(0xffffffffu, __popc(bitsA));
+                    cb = __reduce_add_sync(0xffffffffu, __popc(bitsB));
+                }
+                if (lane == 0) {
+                    p.tcount[tA] = (uint32_t)ca;
+                    if (has2) p.tcount[tB] = (uint32_t)cb;
+                    if (!more_chunks && p.counts_out != nullptr) {  // degree in caller order (tpos.w = entry)
+                        p.counts_out[real_to_bits(tpA.w)] = ca;
+                        if (has2) p.counts_out[real_to_bits(tpB.w)] = cb;
+                    }
+                }
+                if (!more_chunks) warp_max_degree = max(warp_max_degree, max(ca, has2 ? cb : 0));
+            }
+          } else {
 #pragma unroll
           for (int yr = 0; yr < 2; yr++) {
             const uint32_t t0 = tb[yr], t1 = te[yr];
@@ -842,63 +1016,7 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                     prodA = (int)p.tcount[t];
                     prodB = has2 ? (int)p.tcount[t + 1] : 0;
                 }
-                if (MODE == MODE_COUNT && write_masks) {
-                    // lane l keeps, for each of its candidates l, 32 + l, 64 + l, ..., one hit bit per target;
-                    // the bits are stored so that the edge-writing pass need not repeat the distance tests
-                    unsigned short* mrowA = p.hitmask + (size_t)t * 32;
-                    unsigned short* mrowB = p.hitmask + (size_t)(has2 ? t + 1 : t) * 32;
-                    uint32_t bitsA = 0, bitsB = 0;
-                    if (chunk != 0) {
-                        bitsA = mrowA[lane];
-                        bitsB = mrowB[lane];
-                    }
-                    uint32_t bit = 1u << (cbeg >> 5);
-#pragma unroll COUNT_UNROLL
-                    for (int k = 0; k < clen32; k += 32) {
-                        const Vec4<T> c = cand[k + lane];
-                        const T sx = c.x, sy = c.y, sz = c.z;
-                        const T dA = (ax - sx) * (ax - sx) + (ay - sy) * (ay - sy) + (az - sz) * (az - sz);
-                        const T dB = (bx - sx) * (bx - sx) + (by - sy) * (by - sy) + (bz - sz) * (bz - sz);
-                        bitsA |= ((dA <= r2) && (dA > eps)) ? bit : 0u;
-                        bitsB |= ((dB <= r2) && (dB > eps)) ? bit : 0u;
-                        bit <<= 1;
-                    }
-                    mrowA[lane] = (unsigned short)bitsA;
-                    if (has2) mrowB[lane] = (unsigned short)bitsB;
-                    const int ca = __reduce_add_sync(0xffffffffu, __popc(bitsA));
-                    const int cb = __reduce_add_sync(0xffffffffu, __popc(bitsB));
-                    if (lane == 0) {
-                        p.tcount[t] = (uint32_t)ca;
-                        if (has2) p.tcount[t + 1] = (uint32_t)cb;
-                        if (!more_chunks && p.counts_out != nullptr) {  // degree in caller order (tpos.w = entry)
-                            p.counts_out[real_to_bits(tpA.w)] = ca;
-                            if (has2) p.counts_out[real_to_bits(tpB.w)] = cb;
-                        }
-                    }
-                    if (!more_chunks) warp_max_degree = max(warp_max_degree, max(ca, has2 ? cb : 0));
-                } else if (MODE == MODE_COUNT) {
-                    int ca = 0, cb = 0;
-#pragma unroll 2
-                    for (int k = 0; k < clen32; k += 32) {
-                        const Vec4<T> c = cand[k + lane];
-                        const T sx = c.x, sy = c.y, sz = c.z;
-                        const T dA = (ax - sx) * (ax - sx) + (ay - sy) * (ay - sy) + (az - sz) * (az - sz);
-                        const T dB = (bx - sx) * (bx - sx) + (by - sy) * (by - sy) + (bz - sz) * (bz - sz);
-                        ca += ((dA <= r2) && (dA > eps)) ? 1 : 0;
-                        cb += ((dB <= r2) && (dB > eps)) ? 1 : 0;
-                    }
-                    ca = __reduce_add_sync(0xffffffffu, ca);
-                    cb = __reduce_add_sync(0xffffffffu, cb);
-                    if (lane == 0) {
-                        p.tcount[t] = (uint32_t)(prodA + ca);
-                        if (has2) p.tcount[t + 1] = (uint32_t)(prodB + cb);
-                        if (!more_chunks && p.counts_out != nullptr) {
-                            p.counts_out[real_to_bits(tpA.w)] = prodA + ca;
-                            if (has2) p.counts_out[real_to_bits(tpB.w)] = prodB + cb;
-                        }
-                    }
-                    if (!more_chunks) warp_max_degree = max(warp_max_degree, max(prodA + ca, has2 ? prodB + cb : 0));
-                } else {
+                {
                     int4 tmA = p.tmeta[t];
                     int4 tmB = p.tmeta[has2 ? t + 1 : t];
                     long long baseA = 0, baseB = 0, ownA = 0, ownB = 0;
@@ -914,9 +1032,8 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                     for (int k = 0; k < clen32; k += 32) {
                         const int j = k + lane;
                         const Vec4<T> c = cand[j];
-                        const T sx = c.x, sy = c.y, sz = c.z;
-                        const T dA = (ax - sx) * (ax - sx) + (ay - sy) * (ay - sy) + (az - sz) * (az - sz);
-                        const T dB = (bx - sx) * (bx - sx) + (by - sy) * (by - sy) + (bz - sz) * (bz - sz);
+                        const T dA = dist2<T>(ax, ay, az, c.x, c.y, c.z);
+                        const T dB = dist2<T>(bx, by, bz, c.x, c.y, c.z);
                         const bool hitA = (dA <= r2) && (dA > eps);
                         const bool hitB = has2 && (dB <= r2) && (dB > eps);
                         if (MODE == MODE_HALO) {
@@ -965,8 +1082,7 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
                                                    (int)((code >> 20) & 1023u) - 512 + tm.w);
                                         if (d2out != nullptr) {
                                             const T tx = sel ? bx : ax, ty = sel ? by : ay, tz = sel ? bz : az;
-                                            const T hx = ch.x, hy = ch.y, hz = ch.z;
-                                            d2out[e] = (tx - hx) * (tx - hx) + (ty - hy) * (ty - hy) + (tz - hz) * (tz - hz);
+                                            d2out[e] = dist2<T>(tx, ty, tz, ch.x, ch.y, ch.z);
                                         }
                                     }
                                 }
@@ -991,6 +1107,7 @@ rg_pair_kernel(const PairParams<T>* __restrict__ params_dev, long long* __restri
             }
           }
         }
+          }
         // a group whose neighbourhood holds no source at all still owes its targets a zero
         if (MODE == MODE_COUNT && L == 0) {
             for (int yr = 0; yr < 2; yr++)
@@ -1178,7 +1295,7 @@ __global__ void rg_zero_counts_kernel(int64_t Nt, int32_t* counts_out)
 static int pair_grid_waves() { return PAIR_GRID_WAVES; }
 
 struct RgLayout {
-    int64_t hdr, partials, tpartials, posw, aff, ccount, cfill, tccount, tcfill, skey, scell, spos, scode, smeta, hitmask, tkey, tcell, tpos, tmeta,
+    int64_t hdr, partials, tpartials, posw, aff, ccount, cfill, tccount, tcfill, skey, scell, spos, sxyz, scode, smeta, hitmask, tkey, tcell, tpos, tmeta,
         tcount, toffset, sums, total;
 };
 
@@ -1201,6 +1318,7 @@ static RgLayout rg_layout(int64_t N, int64_t Nt, int64_t src_cap, int64_t cell_c
     L.skey = take(src_cap * 8);
     L.scell = take(src_cap * 4);
     L.spos = take(src_cap * v4);
+    L.sxyz = take(dtype == DYNB_F64 ? 0 : src_cap * 12);  // fp32 only: x[], y[], z[] of the source records for the count pass
     L.scode = take(src_cap * 4);
     L.smeta = take(src_cap * 8);
     L.hitmask = take(Nt * 32 * 2);
@@ -1324,6 +1442,7 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
     auto* skey = reinterpret_cast<unsigned long long*>(w + L.skey);
     auto* scell = reinterpret_cast<uint32_t*>(w + L.scell);
     auto* spos = reinterpret_cast<Vec4<T>*>(w + L.spos);
+    float* sxyz = (sizeof(T) == 4) ? reinterpret_cast<float*>(w + L.sxyz) : nullptr;
     auto* scode = reinterpret_cast<uint32_t*>(w + L.scode);
     auto* smeta = reinterpret_cast<uint2*>(w + L.smeta);
     auto* hitmask = reinterpret_cast<unsigned short*>(w + L.hitmask);
@@ -1341,13 +1460,15 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
     static_assert(RG_PARAMS_OFFSET + sizeof(PairParams<T>) <= RG_HEADER_BYTES, "params overflow header block");
     unsigned char init[RG_HEADER_BYTES];
     memset(init, 0, sizeof(init));
+    PairParams<T> pp_host;
+    memset(&pp_host, 0, sizeof(pp_host));
     {
         DevHeader hi;
         memset(&hi, 0, sizeof(hi));
         for (int k = 0; k < 3; k++) { hi.bb_min[k] = ~0ull; hi.bb_max[k] = 0ull; }
         memcpy(init, &hi, sizeof(hi));
-        PairParams<T> pp;
-        pp.h = h; pp.cstart = ccount; pp.tcstart = tccount; pp.spos = spos; pp.scode = scode; pp.smeta = smeta; pp.hitmask = hitmask; pp.counts_out = counts_out; pp.tpos = tpos;
+        PairParams<T>& pp = pp_host;
+        pp.h = h; pp.cstart = ccount; pp.tcstart = tccount; pp.spos = spos; pp.sxyz = sxyz; pp.sxyz_stride = src_cap; pp.scode = scode; pp.smeta = smeta; pp.hitmask = hitmask; pp.counts_out = counts_out; pp.tpos = tpos;
         pp.tmeta = tmeta; pp.tcount = tcount; pp.toffset = toffset; pp.r2 = (T)radius * (T)radius;
         // the targets' fill counters are free once the targets are binned: they hold the list of groups with targets
         pp.glist = (targets != nullptr) ? tcfill : nullptr;
@@ -1387,14 +1508,14 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
         N, Nt, targets, g, posw, h, ccount, cfill, tccount, tcfill, skey, scell, tkey, tcell);
     const int64_t nf = std::max(src_cap, Nt);
     rg_bin_finalize_kernel<T><<<(unsigned)((nf + 255) / 256), 256, 0, stream>>>(
-        N, Nt, targets, g, posw, aff, h, ccount, tccount, skey, scell, tkey, tcell, spos, scode, smeta, tpos, tmeta);
+        N, Nt, targets, g, posw, aff, h, ccount, tccount, skey, scell, tkey, tcell, spos, sxyz, src_cap, scode, smeta, tpos, tmeta);
 
     if (targets != nullptr)
         rg_group_list_kernel<T><<<sm_count_cached() * 8, 256, 0, stream>>>(params_dev, tcfill);
     const int smem = PAIR_WARPS * PAIR_WARP_BYTES;
-    DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_COUNT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_COUNT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int grid = sm_count_cached() * 4 * pair_grid_waves();
-    rg_pair_kernel<T, MODE_COUNT><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, nullptr, nullptr, nullptr, 0, HaloArgs{}, 0, GlueArgs{});
+    rg_pair_kernel<T, MODE_COUNT, true><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, pp_host, nullptr, nullptr, nullptr, 0, HaloArgs{}, 0, GlueArgs{});
     DYNB_CUDA_OK((exclusive_scan<uint32_t, long long>(tcount, toffset, nullptr, Nt + 1, sums64,
                                                        reinterpret_cast<long long*>(&h->E), stream)));
     DYNB_CUDA_OK(cudaGetLastError());
@@ -1409,7 +1530,7 @@ static int rg_fill(const void* ws, int64_t* ei, float* shifts, void* d2out, int6
     const unsigned char* w = static_cast<const unsigned char*>(ws);
     const auto* params_dev = reinterpret_cast<const PairParams<T>*>(w + RG_PARAMS_OFFSET);
     const int smem = PAIR_WARPS * PAIR_WARP_BYTES;
-    DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_FILL>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_FILL, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int grid = sm_count_cached() * 4 * pair_grid_waves();
     GlueArgs glue{};
     if (glue_opt != nullptr) glue = *glue_opt;
@@ -1429,8 +1550,8 @@ static int rg_fill(const void* ws, int64_t* ei, float* shifts, void* d2out, int6
     }
     // behind the bit-driven writer this launch only has the listed long groups to do (usually none): two waves keep its cost low
     const int fgrid = use_masks ? sm_count_cached() * 4 * std::min(2, pair_grid_waves()) : grid;
-    rg_pair_kernel<T, MODE_FILL><<<fgrid, PAIR_THREADS, smem, stream>>>(
-        params_dev, reinterpret_cast<long long*>(ei), shifts, static_cast<T*>(d2out), (long long)E, HaloArgs{}, use_masks, glue);
+    rg_pair_kernel<T, MODE_FILL, false><<<fgrid, PAIR_THREADS, smem, stream>>>(
+        params_dev, PairParams<T>{}, reinterpret_cast<long long*>(ei), shifts, static_cast<T*>(d2out), (long long)E, HaloArgs{}, use_masks, glue);
     DYNB_CUDA_OK(cudaGetLastError());
     return DYNB_OK;
 }
@@ -1441,9 +1562,9 @@ static int rg_halo_mark(const void* ws, const HaloArgs& ha, cudaStream_t stream)
     const unsigned char* w = static_cast<const unsigned char*>(ws);
     const auto* params_dev = reinterpret_cast<const PairParams<T>*>(w + RG_PARAMS_OFFSET);
     const int smem = PAIR_WARPS * PAIR_WARP_BYTES;
-    DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_HALO>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    DYNB_CUDA_OK(cudaFuncSetAttribute(rg_pair_kernel<T, MODE_HALO, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int grid = sm_count_cached() * 4 * pair_grid_waves();
-    rg_pair_kernel<T, MODE_HALO><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, nullptr, nullptr, nullptr, 0, ha, 0, GlueArgs{});
+    rg_pair_kernel<T, MODE_HALO, false><<<grid, PAIR_THREADS, smem, stream>>>(params_dev, PairParams<T>{}, nullptr, nullptr, nullptr, 0, ha, 0, GlueArgs{});
     DYNB_CUDA_OK(cudaGetLastError());
     return DYNB_OK;
 }
