@@ -163,6 +163,7 @@ __device__ __forceinline__ void dist2_x2(unsigned long long ax2, unsigned long l
     asm("mov.b64 {%0, %1}, %2;" : "=f"(d_lo), "=f"(d_hi) : "l"(d));
 }
 
+constexpr int RG_MASK_SLOTS = 16;  // hit bits kept per lane and target (candidate lists up to 512 records)
 constexpr int WRAP_THREADS = 256;
 
 template <typename T>
@@ -457,16 +458,21 @@ rg_grid_kernel(DevHeader* h, double radius, long long src_capacity, long long ce
     // cells per warp work item (Sx along x, Sy along y): as many target cells as possible while the
     // expected dense candidate list stays within 1.5 shared-memory lists
     const double avg = (double)h->M / (double)ncell;
-    // measured on B200 (1 M-atom liquid, 1 M-atom fcc): 2 x 2 cells per warp is best even when the
-    // candidate list then needs a second chunk; fall back to 2 x 1 and 1 x 1 for denser cells
+    // measured on B200 (1 M-atom liquid, 1 M-atom fcc): 2 x 2 cells per warp beat 2 x 1 and 1 x 1 even when the
+    // candidate list then needs a second chunk, and wider groups (3 or 4 cells along x, which lengthens every
+    // candidate run instead of adding runs) beat 2 x 2 as long as the list keeps its hit bits: the work per group
+    // (decode, run table, staging) is shared by more targets.  A list longer than the hit bits sends its group to
+    // the slow writer, so the wide shapes are taken only with a margin (15 % on the mean density, four standard
+    // deviations of a Poisson count) under that limit.
     const double budget = 1.5 * (double)cand_capacity;
-    const int shapes[3][2] = {{2, 2}, {2, 1}, {1, 1}};
+    const int shapes[5][2] = {{4, 2}, {3, 2}, {2, 2}, {2, 1}, {1, 1}};
     int bestx = 1, besty = 1;
-    for (int c = 0; c < 3; c++) {
+    for (int c = 0; c < 5; c++) {
         const int sx = shapes[c][0], sy = shapes[c][1];
         if ((sy + 2 * pad) * (2 * pad + 1) > 32) continue;  // one lane per candidate run
         const double Lexp = (double)(sx + 2 * pad) * (double)(sy + 2 * pad) * (double)(2 * pad + 1) * (avg > 1e-6 ? avg : 1e-6);
-        if (Lexp <= budget || c == 2) { bestx = sx; besty = sy; break; }
+        const bool fits = (sx > 2) ? (1.15 * Lexp + 4.0 * sqrt(Lexp) <= (double)(RG_MASK_SLOTS * 32)) : (Lexp <= budget);
+        if (fits || c == 4) { bestx = sx; besty = sy; break; }
     }
     if (force_sx > 0) bestx = force_sx;
     if (force_sy > 0 && (force_sy + 2 * pad) * (2 * pad + 1) <= 32) besty = force_sy;
@@ -673,7 +679,6 @@ struct HaloArgs {
 #define DYNB_COUNT_UNROLL 1
 #endif
 constexpr int COUNT_UNROLL = DYNB_COUNT_UNROLL;  // unroll factor of the count pass's test loop (tuning knob at build time)
-constexpr int RG_MASK_SLOTS = 16;  // hit bits kept per lane and target (candidate lists up to 512 records)
 
 // Optional extras of the edge writers for the model-side glue: the shifts written with the caller's sign
 // and the Cartesian shift of every edge, unit_shift @ cell, rounded like a K = 3 float GEMM
