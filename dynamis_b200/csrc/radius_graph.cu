@@ -1288,10 +1288,20 @@ rg_fillmask_kernel(const PairParams<T>* __restrict__ params_dev, long long* __re
     }
 }
 
-__global__ void rg_zero_counts_kernel(int64_t Nt, int32_t* counts_out)
+// First launch of a plan: the header block (it travels as a kernel argument: no staging copy of a pageable host
+// buffer), the cell counters, the degree counters and the caller's degree array in one pass.
+struct HeaderBlock { uint32_t words[RG_HEADER_BYTES / 4]; };
+__global__ void __launch_bounds__(256)
+rg_init_kernel(uint32_t* __restrict__ hdr, const HeaderBlock blk, uint4* __restrict__ zero_a, int64_t n_a16,
+               uint4* __restrict__ zero_b, int64_t n_b16, int32_t* __restrict__ counts_out, int64_t Nt)
 {
-    const int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (k < Nt) counts_out[k] = 0;
+    const int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
+    if (i0 < RG_HEADER_BYTES / 4) hdr[i0] = blk.words[i0];
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    for (int64_t i = i0; i < n_a16; i += stride) zero_a[i] = z;
+    for (int64_t i = i0; i < n_b16; i += stride) zero_b[i] = z;
+    if (counts_out != nullptr)
+        for (int64_t i = i0; i < Nt; i += stride) counts_out[i] = 0;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1480,12 +1490,15 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
         pp.long_list = cfill;   // likewise free once the sources are binned
         memcpy(init + RG_PARAMS_OFFSET, &pp, sizeof(pp));
     }
-    // Small pageable source: cudaMemcpyAsync stages it before returning, so the stack buffer may die.
-    DYNB_CUDA_OK(cudaMemcpyAsync(w + L.hdr, init, sizeof(init), cudaMemcpyHostToDevice, stream));
-    DYNB_CUDA_OK(cudaMemsetAsync(w + L.ccount, 0, (size_t)(L.partials - L.ccount), stream));
-    DYNB_CUDA_OK(cudaMemsetAsync(w + L.tcount, 0, (size_t)((Nt + 1) * 4), stream));
-    if (counts_out != nullptr && Nt > 0)
-        rg_zero_counts_kernel<<<(unsigned)((Nt + 255) / 256), 256, 0, stream>>>(Nt, counts_out);
+    {
+        HeaderBlock blk;
+        memcpy(blk.words, init, sizeof(init));
+        // every region of the layout starts on a 256-byte boundary and is padded to one
+        const int64_t n_a16 = (L.partials - L.ccount) / 16, n_b16 = ((Nt + 1) * 4 + 15) / 16;
+        rg_init_kernel<<<sm_count_cached() * 4, 256, 0, stream>>>(reinterpret_cast<uint32_t*>(w + L.hdr), blk,
+                                                                  reinterpret_cast<uint4*>(w + L.ccount), n_a16,
+                                                                  reinterpret_cast<uint4*>(w + L.tcount), n_b16, counts_out, Nt);
+    }
 
     const int vec_ok = (reinterpret_cast<uintptr_t>(pos_dev) % 16 == 0) ? 1 : 0;
     rg_wrap_kernel<T><<<(unsigned)((N + WRAP_THREADS - 1) / WRAP_THREADS), WRAP_THREADS, 0, stream>>>(

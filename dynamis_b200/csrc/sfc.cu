@@ -465,6 +465,75 @@ __device__ void sel_pick_warp(int s, const SelSplit* __restrict__ st_in, SelSpli
     }
 }
 
+// Early finish.  From the second level on the atoms that still share a split point's prefix are few (a million
+// Morton keys spread over 2^14 first digits leave a few hundred), so the level's pass also appends them — full
+// composite number, weight, group — to a short list, and the block that finishes last settles every split point
+// from that list at once: the split atom of a group is the listed atom with the smallest composite number whose
+// inclusive prefix weight inside the group reaches the split point's residual.  The remaining levels then return
+// at once.  A list that overflows, or a group with more than SEL_FINISH_GROUP_MAX atoms, leaves the level as it
+// was and the next level tries again.
+struct SelCand { unsigned long long hi, lo; long long w; int g; int pad; };
+static_assert(sizeof(SelCand) == sizeof(SelSplit), "candidates share the unused split-point slots");
+constexpr int SEL_FINISH_SPLITS = 16;        // the fused path's limit on split points
+constexpr int SEL_CAND_CAP = SEL_MAX_SPLITS - SEL_FINISH_SPLITS;   // records behind the split points of state buffer 0
+constexpr int SEL_FINISH_GROUP_MAX = 256;
+
+__device__ __forceinline__ SelCand sel_load_cand(const SelCand* p)
+{
+    const ulonglong2 a = __ldcg(reinterpret_cast<const ulonglong2*>(p));
+    const ulonglong2 b = __ldcg(reinterpret_cast<const ulonglong2*>(p) + 1);
+    SelCand c;
+    c.hi = a.x; c.lo = a.y; c.w = (long long)b.x; c.g = (int)(unsigned)(b.y & 0xffffffffull); c.pad = 0;
+    return c;
+}
+
+// One warp settles split point s from the candidate list; member[] is the warp's scratch (SEL_FINISH_GROUP_MAX
+// entries).  Returns false (to all lanes) if the group is too large or no listed atom reaches the residual.
+__device__ bool sel_finish_warp(const SelSplit& me, int g, const SelCand* cand, int total, unsigned short* member, SelSplit* out)
+{
+    const int lane = threadIdx.x & 31;
+    const unsigned lt = lanemask_lt();
+    int m = 0;
+    for (int base = 0; base < total; base += 32) {
+        const int i = base + lane;
+        bool in = false;
+        if (i < total) in = ((int)(unsigned)(__ldcg(reinterpret_cast<const unsigned long long*>(cand + i) + 3) & 0xffffffffull) == g);
+        const unsigned mm = __ballot_sync(0xffffffffu, in);
+        if (in) {
+            const int at = m + __popc(mm & lt);
+            if (at < SEL_FINISH_GROUP_MAX) member[at] = (unsigned short)i;
+        }
+        m += __popc(mm);
+    }
+    __syncwarp();
+    if (m == 0 || m > SEL_FINISH_GROUP_MAX) return false;
+    u128 best = ~(u128)0;
+    for (int a = lane; a < m; a += 32) {
+        const SelCand ca = sel_load_cand(cand + member[a]);
+        const u128 Ca = ((u128)ca.hi << 64) | (u128)ca.lo;
+        long long inc = 0;
+        for (int b = 0; b < m; b++) {
+            const SelCand cb = sel_load_cand(cand + member[b]);
+            const u128 Cb = ((u128)cb.hi << 64) | (u128)cb.lo;
+            if (Cb <= Ca) inc += cb.w;
+        }
+        if (inc >= me.residual && Ca < best) best = Ca;
+    }
+    unsigned long long bh = (unsigned long long)(best >> 64), bl = (unsigned long long)best;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long oh = __shfl_xor_sync(0xffffffffu, bh, o), ol = __shfl_xor_sync(0xffffffffu, bl, o);
+        if (oh < bh || (oh == bh && ol < bl)) { bh = oh; bl = ol; }
+    }
+    if (bh == ~0ull && bl == ~0ull) return false;
+    if (lane == 0) {
+        SelSplit r = me;
+        r.pre_hi = bh; r.pre_lo = bl; r.residual = 0;
+        *out = r;
+    }
+    return true;
+}
+
 // Table of one level: per group 2^dbits digit counters ("fine"), followed by per group 256 coarse
 // counters, one per run of 2^fbits consecutive digits (fbits = min(width, 8)), so that a split point is
 // located by reading 256 + 256 counters instead of the whole digit range.
@@ -475,7 +544,8 @@ sel_hist_kernel(const uint64_t* __restrict__ keys, const int64_t* __restrict__ w
                 int shift, int width, int dbits, const SelSplit* __restrict__ st, SelSplit* __restrict__ st_out, int nsplit,
                 int level, int64_t W, const long long* __restrict__ thresholds, unsigned long long* __restrict__ hist,
                 unsigned long long* __restrict__ hist_next, int64_t table_words, unsigned int* __restrict__ done_counter,
-                int fine_private)
+                int fine_private, SelCand* __restrict__ cand, unsigned int* __restrict__ cand_count,
+                unsigned int* __restrict__ finished, SelSplit* __restrict__ st_other)
 {
     // fine_private (first level, unit weights, width <= 14 only): the digit counters of this block are kept in
     // shared memory and added to the table once at the end -- for keys that crowd into a few digits (the
@@ -485,6 +555,8 @@ sel_hist_kernel(const uint64_t* __restrict__ keys, const int64_t* __restrict__ w
     __shared__ int gid[SEL_MAX_SPLITS];
     __shared__ unsigned long long s_coarse[256];
     __shared__ bool s_last;
+    // cand != nullptr: the early finish is in use (see above); finished: set by the level that settled the split points
+    if (cand != nullptr && __ldcg(finished) != 0u) return;
     // clear the table the next level accumulates into (its last reader, the previous pick, has finished)
     for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < table_words; k += (int64_t)gridDim.x * blockDim.x)
         hist_next[k] = 0ull;
@@ -510,8 +582,9 @@ sel_hist_kernel(const uint64_t* __restrict__ keys, const int64_t* __restrict__ w
             size_t slot = ~(size_t)0;  // counter of this atom, or none
             unsigned digit = 0;
             int lo = 0;
+            u128 C = 0;
             if (i < n) {
-                const u128 C = ((u128)keys[i] << idx_bits) | (u128)(uint64_t)i;
+                C = ((u128)keys[i] << idx_bits) | (u128)(uint64_t)i;
                 const u128 P = C >> (shift + width);
                 int hi = ng;  // first group with prefix >= P
                 while (lo < hi) {
@@ -523,6 +596,22 @@ sel_hist_kernel(const uint64_t* __restrict__ keys, const int64_t* __restrict__ w
                     if (w) {
                         digit = (unsigned)((C >> shift) & dmask);
                         slot = ((size_t)lo << dbits) + digit;
+                    }
+                }
+            }
+            if (cand != nullptr && level > 0) {
+                // the atoms counted at this level, listed for the early finish (one atomic per warp round)
+                const bool listed = (slot != ~(size_t)0);
+                const unsigned lm = __ballot_sync(0xffffffffu, listed);
+                if (lm) {
+                    const int leader = __ffs((int)lm) - 1;
+                    unsigned at = 0;
+                    if ((int)(threadIdx.x & 31) == leader) at = atomicAdd(cand_count, (unsigned)__popc(lm));
+                    at = __shfl_sync(0xffffffffu, at, leader) + (unsigned)__popc(lm & lanemask_lt());
+                    if (listed && at < (unsigned)SEL_CAND_CAP) {
+                        SelCand c;
+                        c.hi = (unsigned long long)(C >> 64); c.lo = (unsigned long long)C; c.w = (long long)w; c.g = lo; c.pad = 0;
+                        cand[at] = c;
                     }
                 }
             }
@@ -559,6 +648,30 @@ sel_hist_kernel(const uint64_t* __restrict__ keys, const int64_t* __restrict__ w
     __threadfence();
     for (int s = threadIdx.x >> 5; s < nsplit; s += (int)(blockDim.x >> 5))
         sel_pick_warp(s, st, st_out, gid, nsplit, level, width, dbits, n, W, weights != nullptr ? 1 : 0, thresholds, hist);
+    if (cand == nullptr || level == 0 || nsplit > SEL_FINISH_SPLITS) return;
+    // early finish: settle every split point from the list, or leave the level's result as it is
+    __shared__ SelSplit s_fin[SEL_FINISH_SPLITS];
+    __shared__ unsigned short s_member[8][SEL_FINISH_GROUP_MAX];
+    __shared__ int s_fail;
+    if (threadIdx.x == 0) s_fail = 0;
+    __syncthreads();
+    const int total = (int)__ldcg(cand_count);
+    if (total > SEL_CAND_CAP) return;
+    for (int s = threadIdx.x >> 5; s < nsplit; s += (int)(blockDim.x >> 5)) {
+        const SelSplit me = st[s];
+        if (me.dead) {
+            if ((threadIdx.x & 31) == 0) s_fin[s] = me;
+        } else if (!sel_finish_warp(me, gid[s], cand, total, s_member[threadIdx.x >> 5], &s_fin[s])) {
+            if ((threadIdx.x & 31) == 0) s_fail = 1;
+        }
+    }
+    __syncthreads();
+    if (s_fail) return;
+    // whichever state buffer the caller reads after the last level holds the settled split points
+    for (int s = threadIdx.x; s < nsplit; s += blockDim.x) { st_out[s] = s_fin[s]; st_other[s] = s_fin[s]; }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) *finished = 1u;
 }
 
 // the same step as its own launch, eight split points per block (many split points)
@@ -628,7 +741,13 @@ int sel_select_splits(const uint64_t* keys, int key_bits, const int64_t* weights
     // the first table and, behind it, one arrival counter per level
     unsigned int* counters = reinterpret_cast<unsigned int*>(hist + table_words);
     DYNB_CUDA_OK(cudaMemsetAsync(hist, 0, (size_t)table_words * 8 + 256, s));
-    const bool fused = nsplit <= 16;  // two rounds of eight warps in the last block
+    const bool fused = nsplit <= SEL_FINISH_SPLITS;  // two rounds of eight warps in the last block
+    // early finish (fused path only): candidates in the split-point slots of state buffer 0 that no level uses,
+    // one list counter per level behind the arrival counters, then the "finished" word
+    SelCand* cand = fused ? reinterpret_cast<SelCand*>(st + SEL_FINISH_SPLITS) : nullptr;
+    unsigned int* cand_counts = counters + 16;
+    unsigned int* finished = counters + 48;
+    if (levels > 16) return fail_arg("too many digit levels");
     const int hgrid = (int)std::min<int64_t>((n + 255) / 256, (int64_t)sm_count_cached() * 4);  // one wave
     for (int l = 0; l < levels; l++) {
         const int width = std::min(dbits, B - l * dbits);
@@ -643,7 +762,8 @@ int sel_select_splits(const uint64_t* keys, int key_bits, const int64_t* weights
         // static + dynamic shared memory beyond 48 KB needs the opt-in
         if (dyn > 0) DYNB_CUDA_OK(cudaFuncSetAttribute(sel_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
         sel_hist_kernel<<<hgrid, 256, dyn, s>>>(keys, weights_dev, n, idx_bits, shift, width, dbits, st_in, st_out, nsplit, l, W,
-                                                thresholds_dev, h_cur, h_other, table_words, done, priv);
+                                                thresholds_dev, h_cur, h_other, table_words, done, priv, cand, cand_counts + l, finished,
+                                                const_cast<SelSplit*>(st_in));
         if (!fused)
             sel_pick_kernel<<<(nsplit + 7) / 8, 256, 0, s>>>(st_in, st_out, nsplit, l, width, dbits, n, W,
                                                              weights_dev != nullptr ? 1 : 0, thresholds_dev, h_cur);

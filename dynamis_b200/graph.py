@@ -151,17 +151,26 @@ def plan_radius_graph(pos, cell, pbc, radius, target_indices=None) -> RadiusGrap
     dev = pos.device
     dtype_code = _lib.DYNB_F64 if pos.dtype == torch.float64 else _lib.DYNB_F32
     np_real = np.float64 if pos.dtype == torch.float64 else np.float32
-    cell_h = np.ascontiguousarray(cell.detach().to("cpu").numpy().astype(np_real))
-    pbc_h = np.ascontiguousarray(pbc.detach().to("cpu").numpy().astype(bool).astype(np.uint8))
-    radius = float(np.float32(radius)) if dtype_code == _lib.DYNB_F32 else float(radius)
+    cell_np = cell.detach().to("cpu").numpy()
+    pbc_np = pbc.detach().to("cpu").numpy()
 
     with torch.cuda.device(dev):
         st = _dev_state(dev)
-        src_cap = ctypes.c_int64()
-        cell_cap = ctypes.c_int64()
-        _lib.check(L.dynb_rg_suggest_capacity(N, cell_h.ctypes.data, pbc_h.ctypes.data, radius, dtype_code,
-                                              ctypes.byref(src_cap), ctypes.byref(cell_cap)), "rg_suggest_capacity")
-        src_cap, cell_cap = src_cap.value, cell_cap.value
+        # the host-side conversions and the capacities of a geometry are kept by value of (cell, pbc, radius, sizes)
+        geo_key = (cell_np.tobytes(), str(cell_np.dtype), pbc_np.tobytes(), float(radius), N, dtype_code)
+        geo = st["geo"].get(geo_key)
+        if geo is None:
+            cell_h = np.ascontiguousarray(cell_np.astype(np_real))
+            pbc_h = np.ascontiguousarray(pbc_np.astype(bool).astype(np.uint8))
+            radius_h = float(np.float32(radius)) if dtype_code == _lib.DYNB_F32 else float(radius)
+            src_cap = ctypes.c_int64()
+            cell_cap = ctypes.c_int64()
+            _lib.check(L.dynb_rg_suggest_capacity(N, cell_h.ctypes.data, pbc_h.ctypes.data, radius_h, dtype_code,
+                                                  ctypes.byref(src_cap), ctypes.byref(cell_cap)), "rg_suggest_capacity")
+            if len(st["geo"]) > 64:
+                st["geo"].clear()
+            geo = st["geo"][geo_key] = (cell_h, pbc_h, radius_h, src_cap.value, cell_cap.value)
+        cell_h, pbc_h, radius, src_cap, cell_cap = geo
         counts = torch.empty((Nt,), dtype=torch.int32, device=dev)
         stream = torch.cuda.current_stream(dev)
         hdr = st["hdr"]
@@ -178,6 +187,7 @@ def plan_radius_graph(pos, cell, pbc, radius, target_indices=None) -> RadiusGrap
             status = int(hdr.status)
             if status & _lib.RG_SRC_OVERFLOW and attempt < 2:
                 src_cap = int(hdr.M) + 1024
+                st["geo"][geo_key] = (cell_h, pbc_h, radius, src_cap, cell_cap)  # the next call starts with the larger capacity
                 continue
             break
     if status & _lib.RG_BAD_TARGET:
@@ -322,10 +332,10 @@ def owned_graph(positions: torch.Tensor, cell: torch.Tensor, pbc: torch.Tensor, 
 
 
 def launches_per_graph() -> int:
-    """Kernels one radius_graph_pbc call launches: zero-degrees, wrap, grid, cell histogram,
-    3 scan kernels (source and target cell starts together), scatter, finalize, count pass (degrees included),
-    3 scan kernels (edge offsets), two edge-writing launches (the one driven by the hit bits of the
+    """Kernels one radius_graph_pbc call launches: init (header, counters, degrees), wrap, grid, cell histogram,
+    2 scan kernels (source and target cell starts together), scatter, finalize, count pass (degrees included),
+    2 scan kernels (edge offsets), two edge-writing launches (the one driven by the hit bits of the
     count pass and the one that recomputes distances; the device decides which of them does the work, the
-    other returns at once; with distances requested only the second is launched).  One more, the target
-    bounding box, with a target subset."""
-    return 15
+    other returns at once; with distances requested only the second is launched).  Two more, the target
+    bounding box and the list of groups with targets, with a target subset."""
+    return 13
