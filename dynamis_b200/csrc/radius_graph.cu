@@ -494,8 +494,7 @@ rg_bin_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ targets, Geom<T
               const Vec4<T>* __restrict__ posw, DevHeader* __restrict__ hp,
               uint32_t* __restrict__ ccount, uint32_t* __restrict__ cfill,
               uint32_t* __restrict__ tccount, uint32_t* __restrict__ tcfill,
-              unsigned long long* __restrict__ skey, uint32_t* __restrict__ scell,
-              uint32_t* __restrict__ tkey, uint32_t* __restrict__ tcell)
+              uint4* __restrict__ srec, uint2* __restrict__ trec)
 {
     const DevHeader h = *hp;
     if (h.status & RG_FATAL) return;
@@ -521,10 +520,12 @@ rg_bin_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ targets, Geom<T
                     if (!SCATTER) {
                         atomicAdd(&ccount[c], 1u);
                     } else {
-                        const uint32_t slot = ccount[c] + atomicAdd(&cfill[c], 1u);
+                        // the fill cursors start at the cells' first slots (the prefix sum wrote them there too):
+                        // one atomic and one 16-byte record {key, cell} per image
+                        const uint32_t slot = atomicAdd(&cfill[c], 1u);
                         const unsigned code = (unsigned)(((dx + g.rep[0]) * k1 + (dy + g.rep[1])) * k2 + (dz + g.rep[2]));
-                        skey[slot] = (unsigned long long)i * K + code;
-                        scell[slot] = c;
+                        const unsigned long long key = (unsigned long long)i * K + code;
+                        srec[slot] = make_uint4((uint32_t)key, (uint32_t)(key >> 32), c, 0u);
                     }
                 }
     }
@@ -538,9 +539,8 @@ rg_bin_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ targets, Geom<T
             if (!SCATTER) {
                 atomicAdd(&tccount[c], 1u);
             } else {
-                const uint32_t slot = tccount[c] + atomicAdd(&tcfill[c], 1u);
-                tkey[slot] = (uint32_t)i;
-                tcell[slot] = c;
+                const uint32_t slot = atomicAdd(&tcfill[c], 1u);
+                trec[slot] = make_uint2((uint32_t)i, c);
             }
         }
     }
@@ -557,20 +557,23 @@ __global__ void __launch_bounds__(256)
 rg_bin_finalize_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ targets, Geom<T> g,
                        const Vec4<T>* __restrict__ posw, const int4* __restrict__ aff,
                        DevHeader* __restrict__ hp, const uint32_t* __restrict__ cstart,
-                       const uint32_t* __restrict__ tcstart, const unsigned long long* __restrict__ skey,
-                       const uint32_t* __restrict__ scell, const uint32_t* __restrict__ tkey,
-                       const uint32_t* __restrict__ tcell, Vec4<T>* __restrict__ spos, float* __restrict__ sxyz, long long sxyz_stride,
+                       const uint32_t* __restrict__ tcstart, const uint4* __restrict__ srec, const uint2* __restrict__ trec,
+                       Vec4<T>* __restrict__ spos, float* __restrict__ sxyz, long long sxyz_stride,
                        uint32_t* __restrict__ scode, uint2* __restrict__ smeta, Vec4<T>* __restrict__ tpos, int4* __restrict__ tmeta)
 {
     const DevHeader h = *hp;
     if (h.status & RG_FATAL) return;
     const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (j < (int64_t)h.M) {
-        const uint32_t c = scell[j];
-        const unsigned long long key = skey[j];
+        const uint4 rec = srec[j];
+        const uint32_t c = rec.z;
+        const unsigned long long key = (unsigned long long)rec.x | ((unsigned long long)rec.y << 32);
         const uint32_t b = cstart[c], e = cstart[c + 1];
         uint32_t rank = 0;
-        for (uint32_t q = b; q < e; q++) rank += (skey[q] < key) ? 1u : 0u;
+        for (uint32_t q = b; q < e; q++) {
+            const uint2 kq = *reinterpret_cast<const uint2*>(&srec[q]);
+            rank += (((unsigned long long)kq.x | ((unsigned long long)kq.y << 32)) < key) ? 1u : 0u;
+        }
         const int k1 = 2 * g.rep[1] + 1, k2 = 2 * g.rep[2] + 1;
         const unsigned long long K = (unsigned long long)(2 * g.rep[0] + 1) * k1 * k2;
         const int64_t atom = (int64_t)(key / K);
@@ -600,11 +603,12 @@ rg_bin_finalize_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ target
         }
     }
     if (j < Nt) {
-        const uint32_t c = tcell[j];
-        const uint32_t ent = tkey[j];
+        const uint2 rec = trec[j];
+        const uint32_t c = rec.y;
+        const uint32_t ent = rec.x;
         const uint32_t b = tcstart[c], e = tcstart[c + 1];
         uint32_t rank = 0;
-        for (uint32_t q = b; q < e; q++) rank += (tkey[q] < ent) ? 1u : 0u;
+        for (uint32_t q = b; q < e; q++) rank += (trec[q].x < ent) ? 1u : 0u;
         const int64_t a = targets ? targets[ent] : (int64_t)ent;
         const Vec4<T> w = posw[a];
         const int4 ff = aff[a];
@@ -1310,7 +1314,7 @@ rg_init_kernel(uint32_t* __restrict__ hdr, const HeaderBlock blk, uint4* __restr
 static int pair_grid_waves() { return PAIR_GRID_WAVES; }
 
 struct RgLayout {
-    int64_t hdr, partials, tpartials, posw, aff, ccount, cfill, tccount, tcfill, skey, scell, spos, sxyz, scode, smeta, hitmask, tkey, tcell, tpos, tmeta,
+    int64_t hdr, partials, tpartials, posw, aff, ccount, cfill, tccount, tcfill, srec, spos, sxyz, scode, smeta, hitmask, trec, tpos, tmeta,
         tcount, toffset, sums, total;
 };
 
@@ -1330,15 +1334,13 @@ static RgLayout rg_layout(int64_t N, int64_t Nt, int64_t src_cap, int64_t cell_c
     L.tpartials = take(((Nt + 255) / 256 + 1) * 64);
     L.posw = take(N * v4);
     L.aff = take(N * 16);
-    L.skey = take(src_cap * 8);
-    L.scell = take(src_cap * 4);
+    L.srec = take(src_cap * 16);  // {key, cell} of every source image, in slot order
     L.spos = take(src_cap * v4);
     L.sxyz = take(dtype == DYNB_F64 ? 0 : src_cap * 12);  // fp32 only: x[], y[], z[] of the source records for the count pass
     L.scode = take(src_cap * 4);
     L.smeta = take(src_cap * 8);
     L.hitmask = take(Nt * 32 * 2);
-    L.tkey = take(Nt * 4);
-    L.tcell = take(Nt * 4);
+    L.trec = take(Nt * 8);        // {entry, cell} of every target, in slot order
     L.tpos = take(Nt * v4);
     L.tmeta = take(Nt * 16);
     L.tcount = take((Nt + 1) * 4);
@@ -1454,15 +1456,13 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
     auto* cfill = reinterpret_cast<uint32_t*>(w + L.cfill);
     auto* tccount = reinterpret_cast<uint32_t*>(w + L.tccount);
     auto* tcfill = reinterpret_cast<uint32_t*>(w + L.tcfill);
-    auto* skey = reinterpret_cast<unsigned long long*>(w + L.skey);
-    auto* scell = reinterpret_cast<uint32_t*>(w + L.scell);
+    auto* srec = reinterpret_cast<uint4*>(w + L.srec);
     auto* spos = reinterpret_cast<Vec4<T>*>(w + L.spos);
     float* sxyz = (sizeof(T) == 4) ? reinterpret_cast<float*>(w + L.sxyz) : nullptr;
     auto* scode = reinterpret_cast<uint32_t*>(w + L.scode);
     auto* smeta = reinterpret_cast<uint2*>(w + L.smeta);
     auto* hitmask = reinterpret_cast<unsigned short*>(w + L.hitmask);
-    auto* tkey = reinterpret_cast<uint32_t*>(w + L.tkey);
-    auto* tcell = reinterpret_cast<uint32_t*>(w + L.tcell);
+    auto* trec = reinterpret_cast<uint2*>(w + L.trec);
     auto* tpos = reinterpret_cast<Vec4<T>*>(w + L.tpos);
     auto* tmeta = reinterpret_cast<int4*>(w + L.tmeta);
     auto* tcount = reinterpret_cast<uint32_t*>(w + L.tcount);
@@ -1517,16 +1517,16 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
 
     const int64_t nb = std::max(N, Nt);
     rg_bin_kernel<T, false><<<(unsigned)((nb + 255) / 256), 256, 0, stream>>>(
-        N, Nt, targets, g, posw, h, ccount, cfill, tccount, tcfill, skey, scell, tkey, tcell);
+        N, Nt, targets, g, posw, h, ccount, cfill, tccount, tcfill, srec, trec);
     // cell starts of sources and targets in the same three launches; the total of the source counts is the
     // number of source images actually binned (<= the count of rg_wrap when clipping): it becomes header.M
     DYNB_CUDA_OK((exclusive_scan_pair<uint32_t, uint32_t>(ccount, ccount, reinterpret_cast<uint32_t*>(&h->M), tccount, tccount, nullptr,
-                                                           &h->ncell_plus1, cell_cap + 1, sums32, stream)));
+                                                           &h->ncell_plus1, cell_cap + 1, sums32, stream, cfill, tcfill)));
     rg_bin_kernel<T, true><<<(unsigned)((nb + 255) / 256), 256, 0, stream>>>(
-        N, Nt, targets, g, posw, h, ccount, cfill, tccount, tcfill, skey, scell, tkey, tcell);
+        N, Nt, targets, g, posw, h, ccount, cfill, tccount, tcfill, srec, trec);
     const int64_t nf = std::max(src_cap, Nt);
     rg_bin_finalize_kernel<T><<<(unsigned)((nf + 255) / 256), 256, 0, stream>>>(
-        N, Nt, targets, g, posw, aff, h, ccount, tccount, skey, scell, tkey, tcell, spos, sxyz, src_cap, scode, smeta, tpos, tmeta);
+        N, Nt, targets, g, posw, aff, h, ccount, tccount, srec, trec, spos, sxyz, src_cap, scode, smeta, tpos, tmeta);
 
     if (targets != nullptr)
         rg_group_list_kernel<T><<<sm_count_cached() * 8, 256, 0, stream>>>(params_dev, tcfill);

@@ -113,7 +113,7 @@ scan_sums_pair_kernel(TOut* __restrict__ sums, int num_tiles, TOut* __restrict__
 
 template <typename TIn, typename TOut>
 __device__ __forceinline__ void scan_apply_body(const TIn* in, const uint32_t* __restrict__ n_dev, int64_t n_host,
-                                                const TOut* __restrict__ sums, TOut* out)
+                                                const TOut* __restrict__ sums, TOut* out, TOut* out_copy = nullptr)
 {
     __shared__ TOut warp_sums[SCAN_THREADS / 32];
     const int64_t n = scan_count(n_dev, n_host);
@@ -129,7 +129,10 @@ __device__ __forceinline__ void scan_apply_body(const TIn* in, const uint32_t* _
     TOut run = block_excl_scan<TOut>(s, &tot, warp_sums) + sums[blockIdx.x];
 #pragma unroll
     for (int i = 0; i < SCAN_ITEMS; i++) {
-        if (base + i < n) out[base + i] = run;
+        if (base + i < n) {
+            out[base + i] = run;
+            if (out_copy != nullptr) out_copy[base + i] = run;
+        }
         run += v[i];
     }
 }
@@ -145,9 +148,10 @@ scan_apply_kernel(const TIn* in, const uint32_t* __restrict__ n_dev, int64_t n_h
 template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(SCAN_THREADS)
 scan_apply_pair_kernel(const TIn* in0, TOut* out0, const TIn* in1, TOut* out1, const uint32_t* __restrict__ n_dev, int64_t n_host,
-                       const TOut* __restrict__ sums)
+                       const TOut* __restrict__ sums, TOut* copy0, TOut* copy1)
 {
-    scan_apply_body<TIn, TOut>(blockIdx.y ? in1 : in0, n_dev, n_host, sums + (size_t)blockIdx.y * gridDim.x, blockIdx.y ? out1 : out0);
+    scan_apply_body<TIn, TOut>(blockIdx.y ? in1 : in0, n_dev, n_host, sums + (size_t)blockIdx.y * gridDim.x, blockIdx.y ? out1 : out0,
+                               blockIdx.y ? copy1 : copy0);
 }
 
 // sum of sums[0 .. blockIdx.x) by the whole block (and, from the last block, the grand total)
@@ -176,7 +180,8 @@ __device__ __forceinline__ TOut scan_prefix_of_sums(const TOut* __restrict__ sum
 
 template <typename TIn, typename TOut>
 __device__ __forceinline__ void scan_apply_fused_body(const TIn* in, const uint32_t* __restrict__ n_dev, int64_t n_host,
-                                                      const TOut* __restrict__ sums, int num_tiles, TOut* out, TOut* total_out)
+                                                      const TOut* __restrict__ sums, int num_tiles, TOut* out, TOut* total_out,
+                                                      TOut* out_copy = nullptr)
 {
     __shared__ TOut warp_sums[SCAN_THREADS / 32];
     const int64_t n = scan_count(n_dev, n_host);
@@ -195,7 +200,10 @@ __device__ __forceinline__ void scan_apply_fused_body(const TIn* in, const uint3
     TOut run = block_excl_scan<TOut>(s, &tot, warp_sums) + before;
 #pragma unroll
     for (int i = 0; i < SCAN_ITEMS; i++) {
-        if (base + i < n) out[base + i] = run;
+        if (base + i < n) {
+            out[base + i] = run;
+            if (out_copy != nullptr) out_copy[base + i] = run;
+        }
         run += v[i];
     }
 }
@@ -211,10 +219,11 @@ scan_apply_fused_kernel(const TIn* in, const uint32_t* __restrict__ n_dev, int64
 template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(SCAN_THREADS)
 scan_apply_fused_pair_kernel(const TIn* in0, TOut* out0, TOut* total0, const TIn* in1, TOut* out1, TOut* total1,
-                             const uint32_t* __restrict__ n_dev, int64_t n_host, const TOut* __restrict__ sums)
+                             const uint32_t* __restrict__ n_dev, int64_t n_host, const TOut* __restrict__ sums, TOut* copy0,
+                             TOut* copy1)
 {
     scan_apply_fused_body<TIn, TOut>(blockIdx.y ? in1 : in0, n_dev, n_host, sums + (size_t)blockIdx.y * gridDim.x, gridDim.x,
-                                     blockIdx.y ? out1 : out0, blockIdx.y ? total1 : total0);
+                                     blockIdx.y ? out1 : out0, blockIdx.y ? total1 : total0, blockIdx.y ? copy1 : copy0);
 }
 
 constexpr int SCAN_FUSED_MAX_TILES = 8192;  // above this the per-block summing of earlier tiles stops being negligible
@@ -242,21 +251,22 @@ static inline cudaError_t exclusive_scan(const TIn* in, TOut* out, const uint32_
     return cudaGetLastError();
 }
 
-// Two arrays of the same (possibly device-side) length in the same three launches.  `sums` must hold
-// 2 x scan_num_tiles(n_host) elements.
+// Two arrays of the same (possibly device-side) length in the same launches.  `sums` must hold
+// 2 x scan_num_tiles(n_host) elements.  copy0 / copy1 (may be null): a second array that receives the same result.
 template <typename TIn, typename TOut>
 static inline cudaError_t exclusive_scan_pair(const TIn* in0, TOut* out0, TOut* total0, const TIn* in1, TOut* out1, TOut* total1,
-                                              const uint32_t* n_dev, int64_t n_host, TOut* sums, cudaStream_t stream)
+                                              const uint32_t* n_dev, int64_t n_host, TOut* sums, cudaStream_t stream,
+                                              TOut* copy0 = nullptr, TOut* copy1 = nullptr)
 {
     if (n_host <= 0) return cudaSuccess;
     const int tiles = scan_num_tiles(n_host);
     scan_tile_sums_pair_kernel<TIn, TOut><<<dim3(tiles, 2), SCAN_THREADS, 0, stream>>>(in0, in1, n_dev, n_host, sums);
     if (tiles <= SCAN_FUSED_MAX_TILES) {
         scan_apply_fused_pair_kernel<TIn, TOut><<<dim3(tiles, 2), SCAN_THREADS, 0, stream>>>(in0, out0, total0, in1, out1, total1, n_dev,
-                                                                                          n_host, sums);
+                                                                                          n_host, sums, copy0, copy1);
     } else {
         scan_sums_pair_kernel<TOut><<<2, SCAN_THREADS, 0, stream>>>(sums, tiles, total0, total1);
-        scan_apply_pair_kernel<TIn, TOut><<<dim3(tiles, 2), SCAN_THREADS, 0, stream>>>(in0, out0, in1, out1, n_dev, n_host, sums);
+        scan_apply_pair_kernel<TIn, TOut><<<dim3(tiles, 2), SCAN_THREADS, 0, stream>>>(in0, out0, in1, out1, n_dev, n_host, sums, copy0, copy1);
     }
     return cudaGetLastError();
 }
