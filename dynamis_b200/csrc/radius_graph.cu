@@ -91,6 +91,9 @@ __device__ __forceinline__ bool finite_t(double a) { return isfinite(a); }
 
 __device__ __forceinline__ unsigned long long ordered_any(float v) { return (unsigned long long)ordered_u32(v); }
 __device__ __forceinline__ unsigned long long ordered_any(double v) { return ordered_u64(v); }
+// the same keys in their natural width: 32 bits for float (one REDUX instruction reduces them over a warp)
+__device__ __forceinline__ uint32_t ordered_key(float v) { return ordered_u32(v); }
+__device__ __forceinline__ unsigned long long ordered_key(double v) { return ordered_u64(v); }
 template <typename T> __device__ __forceinline__ double unordered_any(unsigned long long u);
 template <> __device__ __forceinline__ double unordered_any<float>(unsigned long long u) { return (double)unordered_f32((uint32_t)u); }
 template <> __device__ __forceinline__ double unordered_any<double>(unsigned long long u) { return unordered_f64(u); }
@@ -195,7 +198,8 @@ rg_wrap_kernel(const T* __restrict__ pos, int64_t N, Geom<T> g, int vec_ok, Vec4
     }
     __syncthreads();
 
-    unsigned long long mn[3] = {~0ull, ~0ull, ~0ull}, mx[3] = {0ull, 0ull, 0ull};
+    using Key = typename std::conditional<sizeof(T) == 4, uint32_t, unsigned long long>::type;
+    Key mn[3] = {~(Key)0, ~(Key)0, ~(Key)0}, mx[3] = {0, 0, 0};
     unsigned int count = 0;
     uint32_t status = 0;
 
@@ -229,9 +233,9 @@ rg_wrap_kernel(const T* __restrict__ pos, int64_t N, Geom<T> g, int vec_ok, Vec4
             // interior atom: only its own (0,0,0) image
             T x, y, z;
             image_pos(g, wx, wy, wz, 0, 0, 0, x, y, z);
-            mn[0] = mx[0] = ordered_any(x);
-            mn[1] = mx[1] = ordered_any(y);
-            mn[2] = mx[2] = ordered_any(z);
+            mn[0] = mx[0] = ordered_key(x);
+            mn[1] = mx[1] = ordered_key(y);
+            mn[2] = mx[2] = ordered_key(z);
             count = 1;
         } else if (!(status & DYNB_RG_NONFINITE)) {
             // the images an atom needs form a box of shifts (the flags are per axis and direction): walk
@@ -244,7 +248,7 @@ rg_wrap_kernel(const T* __restrict__ pos, int64_t N, Geom<T> g, int vec_ok, Vec4
                     for (int dz = lo2; dz <= hi2; dz++) {
                         T x, y, z;
                         image_pos(g, wx, wy, wz, dx, dy, dz, x, y, z);
-                        unsigned long long ox = ordered_any(x), oy = ordered_any(y), oz = ordered_any(z);
+                        const Key ox = ordered_key(x), oy = ordered_key(y), oz = ordered_key(z);
                         mn[0] = min(mn[0], ox); mx[0] = max(mx[0], ox);
                         mn[1] = min(mn[1], oy); mx[1] = max(mx[1], oy);
                         mn[2] = min(mn[2], oz); mx[2] = max(mx[2], oz);
@@ -259,19 +263,33 @@ rg_wrap_kernel(const T* __restrict__ pos, int64_t N, Geom<T> g, int vec_ok, Vec4
 
     // block reduction
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
+    if constexpr (sizeof(T) == 4) {
 #pragma unroll
         for (int k = 0; k < 3; k++) {
-            mn[k] = min(mn[k], __shfl_xor_sync(0xffffffffu, mn[k], o));
-            mx[k] = max(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], o));
+            mn[k] = (Key)__reduce_min_sync(0xffffffffu, (unsigned)mn[k]);
+            mx[k] = (Key)__reduce_max_sync(0xffffffffu, (unsigned)mx[k]);
         }
-        count += __shfl_xor_sync(0xffffffffu, count, o);
-        status |= __shfl_xor_sync(0xffffffffu, status, o);
+        count = __reduce_add_sync(0xffffffffu, count);
+        status = __reduce_or_sync(0xffffffffu, status);
+    } else {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+            for (int k = 0; k < 3; k++) {
+                mn[k] = min(mn[k], (Key)__shfl_xor_sync(0xffffffffu, mn[k], o));
+                mx[k] = max(mx[k], (Key)__shfl_xor_sync(0xffffffffu, mx[k], o));
+            }
+            count += __shfl_xor_sync(0xffffffffu, count, o);
+            status |= __shfl_xor_sync(0xffffffffu, status, o);
+        }
     }
     if (lane == 0) {
 #pragma unroll
-        for (int k = 0; k < 3; k++) { red[k][warp] = mn[k]; red[3 + k][warp] = mx[k]; }
+        for (int k = 0; k < 3; k++) {
+            // "no image" stays the 64-bit identity of the minimum that rg_grid_kernel expects
+            red[k][warp] = (mn[k] == ~(Key)0) ? ~0ull : (unsigned long long)mn[k];
+            red[3 + k][warp] = (unsigned long long)mx[k];
+        }
         red_cnt[warp] = count;
         if (status) atomicOr(&h->status, status);
     }
@@ -489,7 +507,7 @@ rg_grid_kernel(DevHeader* h, double radius, long long src_capacity, long long ce
 // binning
 // ------------------------------------------------------------------------------------------
 template <typename T, bool SCATTER>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 5)
 rg_bin_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ targets, Geom<T> g,
               const Vec4<T>* __restrict__ posw, DevHeader* __restrict__ hp,
               uint32_t* __restrict__ ccount, uint32_t* __restrict__ cfill,
@@ -503,7 +521,6 @@ rg_bin_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ targets, Geom<T
         const Vec4<T> w = posw[i];
         const uint32_t flags = (uint32_t)real_to_bits(w.w);
         const int k1 = 2 * g.rep[1] + 1, k2 = 2 * g.rep[2] + 1;
-        const unsigned long long K = (unsigned long long)(2 * g.rep[0] + 1) * k1 * k2;
         // box of needed shifts (see rg_wrap_kernel); same (dx, dy, dz) order as a full walk
         const int lo0 = (flags & 8u) ? -g.rep[0] : 0, hi0 = (flags & 1u) ? g.rep[0] : 0;
         const int lo1 = (flags & 16u) ? -g.rep[1] : 0, hi1 = (flags & 2u) ? g.rep[1] : 0;
@@ -524,8 +541,7 @@ rg_bin_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ targets, Geom<T
                         // one atomic and one 16-byte record {key, cell} per image
                         const uint32_t slot = atomicAdd(&cfill[c], 1u);
                         const unsigned code = (unsigned)(((dx + g.rep[0]) * k1 + (dy + g.rep[1])) * k2 + (dz + g.rep[2]));
-                        const unsigned long long key = (unsigned long long)i * K + code;
-                        srec[slot] = make_uint4((uint32_t)key, (uint32_t)(key >> 32), c, 0u);
+                        srec[slot] = make_uint4(code, (uint32_t)i, c, 0u);  // (atom, shift code) orders the images of a cell
                     }
                 }
     }
@@ -561,61 +577,72 @@ rg_bin_finalize_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ target
                        Vec4<T>* __restrict__ spos, float* __restrict__ sxyz, long long sxyz_stride,
                        uint32_t* __restrict__ scode, uint2* __restrict__ smeta, Vec4<T>* __restrict__ tpos, int4* __restrict__ tmeta)
 {
-    const DevHeader h = *hp;
-    if (h.status & RG_FATAL) return;
+    if (hp->status & RG_FATAL) return;
+    const unsigned long long M = hp->M;
     const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (j < (int64_t)h.M) {
-        const uint4 rec = srec[j];
-        const uint32_t c = rec.z;
-        const unsigned long long key = (unsigned long long)rec.x | ((unsigned long long)rec.y << 32);
-        const uint32_t b = cstart[c], e = cstart[c + 1];
+    const bool has_s = j < (int64_t)M, has_t = j < Nt;
+    // The loads are issued level by level for the source image and the target of this thread together: the two
+    // records, then everything that depends only on a record (cell range, position and floor of the atom), then
+    // the records of the cell for the rank; the kernel waits for memory, not for arithmetic.
+    uint4 srj = make_uint4(0u, 0u, 0u, 0u);
+    uint2 trj = make_uint2(0u, 0u);
+    if (has_s) srj = srec[j];
+    if (has_t) trj = trec[j];
+    uint32_t sb = 0, se = 0, tb = 0, te = 0;
+    Vec4<T> sw = {}, tw = {};
+    int4 sff = make_int4(0, 0, 0, 0), tff = make_int4(0, 0, 0, 0);
+    int64_t ta = 0;
+    if (has_s) {
+        sb = cstart[srj.z];
+        se = cstart[srj.z + 1];
+        sw = posw[srj.y];
+        sff = aff[srj.y];
+    }
+    if (has_t) {
+        tb = tcstart[trj.y];
+        te = tcstart[trj.y + 1];
+        ta = targets ? targets[trj.x] : (int64_t)trj.x;
+        tw = posw[ta];
+        tff = aff[ta];
+    }
+    if (has_s) {
+        const unsigned long long key = ((unsigned long long)srj.y << 32) | srj.x;
         uint32_t rank = 0;
-        for (uint32_t q = b; q < e; q++) {
+        for (uint32_t q = sb; q < se; q++) {
             const uint2 kq = *reinterpret_cast<const uint2*>(&srec[q]);
-            rank += (((unsigned long long)kq.x | ((unsigned long long)kq.y << 32)) < key) ? 1u : 0u;
+            rank += ((((unsigned long long)kq.y << 32) | kq.x) < key) ? 1u : 0u;
         }
         const int k1 = 2 * g.rep[1] + 1, k2 = 2 * g.rep[2] + 1;
-        const unsigned long long K = (unsigned long long)(2 * g.rep[0] + 1) * k1 * k2;
-        const int64_t atom = (int64_t)(key / K);
-        unsigned code = (unsigned)(key % K);
+        const uint32_t atom = srj.y;
+        unsigned code = srj.x;
         const int dz = (int)(code % k2) - g.rep[2]; code /= k2;
         const int dy = (int)(code % k1) - g.rep[1]; code /= k1;
         const int dx = (int)code - g.rep[0];
-        const Vec4<T> w = posw[atom];
-        const int4 ff = aff[atom];
         Vec4<T> r;
-        image_pos(g, w.x, w.y, w.z, dx, dy, dz, r.x, r.y, r.z);
+        image_pos(g, sw.x, sw.y, sw.z, dx, dy, dz, r.x, r.y, r.z);
         r.w = bits_to_real((int32_t)atom, T());
-        spos[b + rank] = r;
+        const uint32_t at = sb + rank;
+        spos[at] = r;
         if (sizeof(T) == 4 && sxyz != nullptr) {
-            sxyz[b + rank] = (float)r.x;
-            sxyz[sxyz_stride + b + rank] = (float)r.y;
-            sxyz[2 * sxyz_stride + b + rank] = (float)r.z;
+            sxyz[at] = (float)r.x;
+            sxyz[sxyz_stride + at] = (float)r.y;
+            sxyz[2 * sxyz_stride + at] = (float)r.z;
         }
-        const int ex = dx - ff.x, ey = dy - ff.y, ez = dz - ff.z;
-        if (ex < -511 || ex > 511 || ey < -511 || ey > 511 || ez < -511 || ez > 511) {
-            atomicOr(&hp->status, DYNB_RG_SHIFT_RANGE);
-            scode[b + rank] = pack_shift_code(0, 0, 0);
-            smeta[b + rank] = make_uint2((uint32_t)atom, pack_shift_code(0, 0, 0));
-        } else {
-            scode[b + rank] = pack_shift_code(ex, ey, ez);
-            smeta[b + rank] = make_uint2((uint32_t)atom, pack_shift_code(ex, ey, ez));
-        }
+        const int ex = dx - sff.x, ey = dy - sff.y, ez = dz - sff.z;
+        uint32_t packed = pack_shift_code(0, 0, 0);
+        if (ex < -511 || ex > 511 || ey < -511 || ey > 511 || ez < -511 || ez > 511) atomicOr(&hp->status, DYNB_RG_SHIFT_RANGE);
+        else packed = pack_shift_code(ex, ey, ez);
+        scode[at] = packed;
+        smeta[at] = make_uint2(atom, packed);
     }
-    if (j < Nt) {
-        const uint2 rec = trec[j];
-        const uint32_t c = rec.y;
-        const uint32_t ent = rec.x;
-        const uint32_t b = tcstart[c], e = tcstart[c + 1];
+    if (has_t) {
+        const uint32_t ent = trj.x;
         uint32_t rank = 0;
-        for (uint32_t q = b; q < e; q++) rank += (trec[q].x < ent) ? 1u : 0u;
-        const int64_t a = targets ? targets[ent] : (int64_t)ent;
-        const Vec4<T> w = posw[a];
-        const int4 ff = aff[a];
+        for (uint32_t q = tb; q < te; q++) rank += (trec[q].x < ent) ? 1u : 0u;
         Vec4<T> r;
-        r.x = w.x; r.y = w.y; r.z = w.z; r.w = bits_to_real((int32_t)ent, T());
-        tpos[b + rank] = r;
-        tmeta[b + rank] = make_int4((int)a, ff.x, ff.y, ff.z);
+        r.x = tw.x; r.y = tw.y; r.z = tw.z; r.w = bits_to_real((int32_t)ent, T());
+        tpos[tb + rank] = r;
+        tmeta[tb + rank] = make_int4((int)ta, tff.x, tff.y, tff.z);
     }
 }
 
