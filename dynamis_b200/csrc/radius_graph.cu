@@ -132,6 +132,112 @@ __device__ __forceinline__ uint32_t cell_of(const DevHeader& h, T x, T y, T z)
     return (uint32_t)cx + (uint32_t)h.nx * ((uint32_t)cy + (uint32_t)h.ny * (uint32_t)cz);
 }
 
+constexpr int RG_MASK_SLOTS = 16;  // hit bits kept per lane and target (candidate lists up to 512 records)
+
+// The cell grid of a plan and the shape of a warp's work item.  Chosen on the device from the bounding box of
+// the data (rg_grid_kernel), or on the host from the cell when the box is periodic in all directions and every
+// atom is a target (the images then fill a known box and the first two passes run as one).
+struct GridChoice {
+    int nx, ny, nz, pad, group_cells, group_cells_y, gx;
+    uint32_t ncell_plus1;
+    unsigned long long num_groups;
+    double gmin[3];
+    double res_inv;
+};
+
+// Cells of edge radius/1.99 scanned +-2 (as the reference, :662,776) unless that would need more than
+// cell_capacity cells; then the cells grow, and once they are wider than the cutoff the scan shrinks to +-1.
+__host__ __device__ inline void rg_choose_shape(GridChoice& gc, double avg, int cand_capacity, int force_sx, int force_sy);
+// avg: expected sources per cell, for the shape of the work items.
+__host__ __device__ inline void rg_choose_grid(const double lo[3], const double ext[3], double radius, long long cell_capacity,
+                                               int cand_capacity, double M, double sources_per_volume, int force_sx, int force_sy,
+                                               GridChoice& gc)
+{
+    double res = radius / 1.99;
+    long long n[3];
+    for (int it = 0; it < 400; it++) {
+        double tot = 1.0;
+        for (int k = 0; k < 3; k++) {
+            double c = ceil(ext[k] / res);
+            if (!(c >= 1.0)) c = 1.0;
+            if (c > 2.0e9) c = 2.0e9;
+            n[k] = (long long)c;
+            tot *= c;
+        }
+        if (tot + 1.0 <= (double)cell_capacity) break;
+        res *= 1.2;
+        if (it == 399) { n[0] = n[1] = n[2] = 1; }
+    }
+    gc.nx = (int)n[0]; gc.ny = (int)n[1]; gc.nz = (int)n[2];
+    const long long ncell = n[0] * n[1] * n[2];
+    gc.ncell_plus1 = (uint32_t)(ncell + 1);
+    const int pad = (res >= radius * 1.001) ? 1 : 2;
+    gc.pad = pad;
+    for (int k = 0; k < 3; k++) gc.gmin[k] = lo[k];
+    gc.res_inv = 1.0 / res;
+    rg_choose_shape(gc, sources_per_volume > 0.0 ? sources_per_volume * res * res * res : M / (double)ncell, cand_capacity, force_sx,
+                    force_sy);
+}
+
+// cells per warp work item (Sx along x, Sy along y): as many target cells as possible while the
+// expected dense candidate list stays within 1.5 shared-memory lists
+__host__ __device__ inline void rg_choose_shape(GridChoice& gc, double avg, int cand_capacity, int force_sx, int force_sy)
+{
+    const int pad = gc.pad;
+    // measured on B200 (1 M-atom liquid, 1 M-atom fcc): 2 x 2 cells per warp beat 2 x 1 and 1 x 1 even when the
+    // candidate list then needs a second chunk, and wider groups (3 or 4 cells along x, which lengthens every
+    // candidate run instead of adding runs) beat 2 x 2 as long as the list keeps its hit bits: the work per group
+    // (decode, run table, staging) is shared by more targets.  A list longer than the hit bits sends its group to
+    // the slow writer, so the wide shapes are taken only with a margin (15 % on the mean density, four standard
+    // deviations of a Poisson count) under that limit.
+    const double budget = 1.5 * (double)cand_capacity;
+    const int shapes[5][2] = {{4, 2}, {3, 2}, {2, 2}, {2, 1}, {1, 1}};
+    int bestx = 1, besty = 1;
+    for (int c = 0; c < 5; c++) {
+        const int sx = shapes[c][0], sy = shapes[c][1];
+        if ((sy + 2 * pad) * (2 * pad + 1) > 32) continue;  // one lane per candidate run
+        const double Lexp = (double)(sx + 2 * pad) * (double)(sy + 2 * pad) * (double)(2 * pad + 1) * (avg > 1e-6 ? avg : 1e-6);
+        const bool fits = (sx > 2) ? (1.15 * Lexp + 4.0 * sqrt(Lexp) <= (double)(RG_MASK_SLOTS * 32)) : (Lexp <= budget);
+        if (fits || c == 4) { bestx = sx; besty = sy; break; }
+    }
+    if (force_sx > 0) bestx = force_sx;
+    if (force_sy > 0 && (force_sy + 2 * pad) * (2 * pad + 1) <= 32) besty = force_sy;
+    if (bestx > gc.nx) bestx = gc.nx;
+    if (besty > gc.ny) besty = gc.ny;
+    gc.group_cells = bestx;
+    gc.group_cells_y = besty;
+    gc.gx = (gc.nx + bestx - 1) / bestx;
+    const int gy = (gc.ny + besty - 1) / besty;
+    gc.num_groups = (unsigned long long)gc.gx * (unsigned long long)gy * (unsigned long long)gc.nz;
+}
+
+__host__ __device__ inline void rg_store_grid(DevHeader& h, const GridChoice& gc)
+{
+    h.nx = gc.nx; h.ny = gc.ny; h.nz = gc.nz;
+    h.ncell_plus1 = gc.ncell_plus1;
+    h.pad = gc.pad;
+    for (int k = 0; k < 3; k++) h.gmin[k] = gc.gmin[k];
+    h.res_inv = gc.res_inv;
+    h.group_cells = gc.group_cells;
+    h.group_cells_y = gc.group_cells_y;
+    h.gx = gc.gx;
+    h.num_groups = gc.num_groups;
+}
+
+// cell_of for a grid that travels as a kernel argument: the same expression on the same numbers
+template <typename T>
+__device__ __forceinline__ uint32_t cell_of(const GridChoice& h, T x, T y, T z)
+{
+    const T ri = (T)h.res_inv;
+    int cx = (int)floor_t((x - (T)h.gmin[0]) * ri);
+    int cy = (int)floor_t((y - (T)h.gmin[1]) * ri);
+    int cz = (int)floor_t((z - (T)h.gmin[2]) * ri);
+    cx = max(0, min(cx, h.nx - 1));
+    cy = max(0, min(cy, h.ny - 1));
+    cz = max(0, min(cz, h.nz - 1));
+    return (uint32_t)cx + (uint32_t)h.nx * ((uint32_t)cy + (uint32_t)h.ny * (uint32_t)cz);
+}
+
 // ------------------------------------------------------------------------------------------
 // rg_wrap
 // ------------------------------------------------------------------------------------------
@@ -166,13 +272,15 @@ __device__ __forceinline__ void dist2_x2(unsigned long long ax2, unsigned long l
     asm("mov.b64 {%0, %1}, %2;" : "=f"(d_lo), "=f"(d_hi) : "l"(d));
 }
 
-constexpr int RG_MASK_SLOTS = 16;  // hit bits kept per lane and target (candidate lists up to 512 records)
 constexpr int WRAP_THREADS = 256;
 
-template <typename T>
+// FUSED: the grid is known before the launch (gc, chosen on the host), so the images and the targets are counted
+// into their cells here and no bounding box is gathered.
+template <typename T, bool FUSED>
 __global__ void __launch_bounds__(WRAP_THREADS)
 rg_wrap_kernel(const T* __restrict__ pos, int64_t N, Geom<T> g, int vec_ok, Vec4<T>* __restrict__ posw,
-               int4* __restrict__ aff, DevHeader* __restrict__ h, unsigned long long* __restrict__ partials)
+               int4* __restrict__ aff, DevHeader* __restrict__ h, unsigned long long* __restrict__ partials,
+               const GridChoice gc, uint32_t* __restrict__ ccount, uint32_t* __restrict__ tccount)
 {
     __shared__ T stage[WRAP_THREADS * 3];
     __shared__ unsigned long long red[6][WRAP_THREADS / 32];
@@ -233,6 +341,7 @@ rg_wrap_kernel(const T* __restrict__ pos, int64_t N, Geom<T> g, int vec_ok, Vec4
             // interior atom: only its own (0,0,0) image
             T x, y, z;
             image_pos(g, wx, wy, wz, 0, 0, 0, x, y, z);
+            if (FUSED) atomicAdd(&ccount[cell_of(gc, x, y, z)], 1u);
             mn[0] = mx[0] = ordered_key(x);
             mn[1] = mx[1] = ordered_key(y);
             mn[2] = mx[2] = ordered_key(z);
@@ -248,6 +357,7 @@ rg_wrap_kernel(const T* __restrict__ pos, int64_t N, Geom<T> g, int vec_ok, Vec4
                     for (int dz = lo2; dz <= hi2; dz++) {
                         T x, y, z;
                         image_pos(g, wx, wy, wz, dx, dy, dz, x, y, z);
+                        if (FUSED) atomicAdd(&ccount[cell_of(gc, x, y, z)], 1u);
                         const Key ox = ordered_key(x), oy = ordered_key(y), oz = ordered_key(z);
                         mn[0] = min(mn[0], ox); mx[0] = max(mx[0], ox);
                         mn[1] = min(mn[1], oy); mx[1] = max(mx[1], oy);
@@ -259,6 +369,8 @@ rg_wrap_kernel(const T* __restrict__ pos, int64_t N, Geom<T> g, int vec_ok, Vec4
         w.x = wx; w.y = wy; w.z = wz; w.w = bits_to_real((int32_t)flags, T());
         posw[i] = w;
         aff[i] = make_int4((int)f[0], (int)f[1], (int)f[2], (int)count);
+        // every atom is a target, binned by its wrapped position (as rg_bin_kernel does)
+        if (FUSED && !(status & DYNB_RG_NONFINITE)) atomicAdd(&tccount[cell_of(gc, wx, wy, wz)], 1u);
     }
 
     // block reduction
@@ -294,6 +406,18 @@ rg_wrap_kernel(const T* __restrict__ pos, int64_t N, Geom<T> g, int vec_ok, Vec4
         if (status) atomicOr(&h->status, status);
     }
     __syncthreads();
+    if (FUSED) {
+        // the bounding box goes straight to the header (it only steers the shape of the work items, which is
+        // settled three launches later): six fire-and-forget atomics per block
+        if (threadIdx.x < 6) {
+            unsigned long long v = red[threadIdx.x][0];
+            for (int w = 1; w < WRAP_THREADS / 32; w++)
+                v = (threadIdx.x < 3) ? min(v, red[threadIdx.x][w]) : max(v, red[threadIdx.x][w]);
+            if (threadIdx.x < 3) atomicMin(&h->bb_min[threadIdx.x], v);
+            else atomicMax(&h->bb_max[threadIdx.x - 3], v);
+        }
+        return;
+    }
     // per-block partial results (bounding box, image count); rg_grid_kernel reduces them, so that no
     // block contends for a handful of header words
     if (threadIdx.x < 6) {
@@ -451,56 +575,9 @@ rg_grid_kernel(DevHeader* h, double radius, long long src_capacity, long long ce
         }
         ext[k] = hi - lo[k];
     }
-    double res = radius / 1.99;
-    long long n[3];
-    for (int it = 0; it < 400; it++) {
-        double tot = 1.0;
-        for (int k = 0; k < 3; k++) {
-            double c = ceil(ext[k] / res);
-            if (!(c >= 1.0)) c = 1.0;
-            if (c > 2.0e9) c = 2.0e9;
-            n[k] = (long long)c;
-            tot *= c;
-        }
-        if (tot + 1.0 <= (double)cell_capacity) break;
-        res *= 1.2;
-        if (it == 399) { n[0] = n[1] = n[2] = 1; }
-    }
-    h->nx = (int)n[0]; h->ny = (int)n[1]; h->nz = (int)n[2];
-    const long long ncell = n[0] * n[1] * n[2];
-    h->ncell_plus1 = (uint32_t)(ncell + 1);
-    const int pad = (res >= radius * 1.001) ? 1 : 2;
-    h->pad = pad;
-    for (int k = 0; k < 3; k++) h->gmin[k] = lo[k];
-    h->res_inv = 1.0 / res;
-    // cells per warp work item (Sx along x, Sy along y): as many target cells as possible while the
-    // expected dense candidate list stays within 1.5 shared-memory lists
-    const double avg = (double)h->M / (double)ncell;
-    // measured on B200 (1 M-atom liquid, 1 M-atom fcc): 2 x 2 cells per warp beat 2 x 1 and 1 x 1 even when the
-    // candidate list then needs a second chunk, and wider groups (3 or 4 cells along x, which lengthens every
-    // candidate run instead of adding runs) beat 2 x 2 as long as the list keeps its hit bits: the work per group
-    // (decode, run table, staging) is shared by more targets.  A list longer than the hit bits sends its group to
-    // the slow writer, so the wide shapes are taken only with a margin (15 % on the mean density, four standard
-    // deviations of a Poisson count) under that limit.
-    const double budget = 1.5 * (double)cand_capacity;
-    const int shapes[5][2] = {{4, 2}, {3, 2}, {2, 2}, {2, 1}, {1, 1}};
-    int bestx = 1, besty = 1;
-    for (int c = 0; c < 5; c++) {
-        const int sx = shapes[c][0], sy = shapes[c][1];
-        if ((sy + 2 * pad) * (2 * pad + 1) > 32) continue;  // one lane per candidate run
-        const double Lexp = (double)(sx + 2 * pad) * (double)(sy + 2 * pad) * (double)(2 * pad + 1) * (avg > 1e-6 ? avg : 1e-6);
-        const bool fits = (sx > 2) ? (1.15 * Lexp + 4.0 * sqrt(Lexp) <= (double)(RG_MASK_SLOTS * 32)) : (Lexp <= budget);
-        if (fits || c == 4) { bestx = sx; besty = sy; break; }
-    }
-    if (force_sx > 0) bestx = force_sx;
-    if (force_sy > 0 && (force_sy + 2 * pad) * (2 * pad + 1) <= 32) besty = force_sy;
-    if (bestx > h->nx) bestx = h->nx;
-    if (besty > h->ny) besty = h->ny;
-    h->group_cells = bestx;
-    h->group_cells_y = besty;
-    h->gx = (h->nx + bestx - 1) / bestx;
-    const int gy = (h->ny + besty - 1) / besty;
-    h->num_groups = (unsigned long long)h->gx * (unsigned long long)gy * (unsigned long long)h->nz;
+    GridChoice gc;
+    rg_choose_grid(lo, ext, radius, cell_capacity, cand_capacity, (double)h->M, 0.0, force_sx, force_sy, gc);
+    rg_store_grid(*h, gc);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -512,10 +589,38 @@ rg_bin_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ targets, Geom<T
               const Vec4<T>* __restrict__ posw, DevHeader* __restrict__ hp,
               uint32_t* __restrict__ ccount, uint32_t* __restrict__ cfill,
               uint32_t* __restrict__ tccount, uint32_t* __restrict__ tcfill,
-              uint4* __restrict__ srec, uint2* __restrict__ trec)
+              uint4* __restrict__ srec, uint2* __restrict__ trec, long long src_capacity, int shape_cand_capacity)
 {
     const DevHeader h = *hp;
     if (h.status & RG_FATAL) return;
+    if (SCATTER && h.M > (unsigned long long)src_capacity) {
+        // more images than the caller's buffers hold (header.M is the prefix sum's total by now; with a grid chosen on
+        // the host this is the first place that knows): nothing is placed, the plan is repeated with a larger capacity
+        if (blockIdx.x == 0 && threadIdx.x == 0) atomicOr(&hp->status, DYNB_RG_SRC_OVERFLOW);
+        return;
+    }
+    if (SCATTER && shape_cand_capacity > 0 && blockIdx.x == 0 && threadIdx.x == 0) {
+        // grid chosen on the host: the shape of the work items is settled here, from the number of images and the
+        // bounding box they really fill (gathered while wrapping) — an atom cluster in a large periodic box is as
+        // dense in its cells as it is, whatever the volume of the cell
+        double vol_cells = 1.0;
+        const double res = 1.0 / h.res_inv;
+        const int nn[3] = {h.nx, h.ny, h.nz};
+        for (int k = 0; k < 3; k++) {
+            const double ext = unordered_any<T>(h.bb_max[k]) - unordered_any<T>(h.bb_min[k]) + 0.02;
+            double cells = ceil(ext / res);
+            if (!(cells >= 1.0)) cells = 1.0;
+            if (cells > (double)nn[k]) cells = (double)nn[k];
+            vol_cells *= cells;
+        }
+        GridChoice gc;
+        gc.nx = h.nx; gc.ny = h.ny; gc.nz = h.nz; gc.pad = h.pad;
+        rg_choose_shape(gc, (double)h.M / vol_cells, shape_cand_capacity, 0, 0);
+        hp->group_cells = gc.group_cells;
+        hp->group_cells_y = gc.group_cells_y;
+        hp->gx = gc.gx;
+        hp->num_groups = gc.num_groups;
+    }
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < N) {
         const Vec4<T> w = posw[i];
@@ -1504,10 +1609,46 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
     memset(init, 0, sizeof(init));
     PairParams<T> pp_host;
     memset(&pp_host, 0, sizeof(pp_host));
+    // Periodic in all directions and every atom a target: the images fill a box that follows from the cell alone
+    // (fractional coordinates in [1 - cf - rep, cf + rep] per axis, see rg_wrap_kernel's flags), so the grid is
+    // chosen here and the first pass counts the images into their cells while it wraps.  Positions that rounding
+    // leaves a hair outside land in the outermost cells (cell_of clamps), which a scan window always includes.
+    GridChoice gc_host;
+    memset(&gc_host, 0, sizeof(gc_host));
+    const bool host_grid = (targets == nullptr) && g.pbc[0] && g.pbc[1] && g.pbc[2];
+    if (host_grid) {
+        double lo[3] = {0, 0, 0}, hi3[3] = {0, 0, 0};
+        for (int d = 0; d < 3; d++) {
+            const double fa = std::max(-(double)g.rep[d], std::min(0.0, 1.0 - (double)g.cf[d] - (double)g.rep[d]));
+            const double fb = std::min(1.0 + (double)g.rep[d], std::max(1.0, (double)g.cf[d] + (double)g.rep[d]));
+            for (int k = 0; k < 3; k++) {
+                const double c = (double)g.cell[3 * d + k];
+                lo[k] += std::min(fa * c, fb * c);
+                hi3[k] += std::max(fa * c, fb * c);
+            }
+        }
+        double ext[3];
+        for (int k = 0; k < 3; k++) {
+            const double slack = 0.01 + 1e-5 * (hi3[k] - lo[k]);
+            lo[k] -= slack;
+            ext[k] = hi3[k] + slack - lo[k];
+        }
+        const double* c = nullptr;
+        double cd[9];
+        for (int k = 0; k < 9; k++) cd[k] = (double)g.cell[k];
+        c = cd;
+        const double vol = std::fabs(c[0] * (c[4] * c[8] - c[5] * c[7]) - c[1] * (c[3] * c[8] - c[5] * c[6]) + c[2] * (c[3] * c[7] - c[4] * c[6]));
+        const double density = vol > 0.0 ? (double)N / vol : 0.0;  // images repeat the atoms: the same density everywhere in the box
+        rg_choose_grid(lo, ext, radius, (long long)cell_cap, PAIR_CAND_BYTES / (int)sizeof(Vec4<T>), (double)N, density, 0, 0, gc_host);
+    }
     {
         DevHeader hi;
         memset(&hi, 0, sizeof(hi));
         for (int k = 0; k < 3; k++) { hi.bb_min[k] = ~0ull; hi.bb_max[k] = 0ull; }
+        if (host_grid) {
+            rg_store_grid(hi, gc_host);
+            for (int k = 0; k < 3; k++) { hi.clip_lo[k] = -1.0e300; hi.clip_hi[k] = 1.0e300; }
+        }
         memcpy(init, &hi, sizeof(hi));
         PairParams<T>& pp = pp_host;
         pp.h = h; pp.cstart = ccount; pp.tcstart = tccount; pp.spos = spos; pp.sxyz = sxyz; pp.sxyz_stride = src_cap; pp.scode = scode; pp.smeta = smeta; pp.hitmask = hitmask; pp.counts_out = counts_out; pp.tpos = tpos;
@@ -1528,29 +1669,35 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
     }
 
     const int vec_ok = (reinterpret_cast<uintptr_t>(pos_dev) % 16 == 0) ? 1 : 0;
-    rg_wrap_kernel<T><<<(unsigned)((N + WRAP_THREADS - 1) / WRAP_THREADS), WRAP_THREADS, 0, stream>>>(
-        static_cast<const T*>(pos_dev), N, g, vec_ok, posw, aff, h, reinterpret_cast<unsigned long long*>(w + L.partials));
-    const int force_sx = 0, force_sy = 0;  // cells per warp work item: chosen on the device
-    int n_tpart = 0;
-    if (targets != nullptr) {
-        n_tpart = (int)((Nt + 255) / 256);
-        rg_target_bbox_kernel<T><<<n_tpart, 256, 0, stream>>>(targets, Nt, N, posw, reinterpret_cast<unsigned long long*>(w + L.tpartials));
-    }
-    rg_grid_kernel<T><<<1, 1024, 0, stream>>>(h, radius, (long long)src_cap, (long long)cell_cap,
-                                             PAIR_CAND_BYTES / (int)sizeof(Vec4<T>), force_sx, force_sy,
-                                             reinterpret_cast<const unsigned long long*>(w + L.partials),
-                                             (int)((N + WRAP_THREADS - 1) / WRAP_THREADS),
-                                             reinterpret_cast<const unsigned long long*>(w + L.tpartials), n_tpart);
-
+    const int force_sx = 0, force_sy = 0;  // cells per warp work item: chosen by rg_choose_grid
     const int64_t nb = std::max(N, Nt);
-    rg_bin_kernel<T, false><<<(unsigned)((nb + 255) / 256), 256, 0, stream>>>(
-        N, Nt, targets, g, posw, h, ccount, cfill, tccount, tcfill, srec, trec);
+    if (host_grid) {
+        rg_wrap_kernel<T, true><<<(unsigned)((N + WRAP_THREADS - 1) / WRAP_THREADS), WRAP_THREADS, 0, stream>>>(
+            static_cast<const T*>(pos_dev), N, g, vec_ok, posw, aff, h, nullptr, gc_host, ccount, tccount);
+    } else {
+        rg_wrap_kernel<T, false><<<(unsigned)((N + WRAP_THREADS - 1) / WRAP_THREADS), WRAP_THREADS, 0, stream>>>(
+            static_cast<const T*>(pos_dev), N, g, vec_ok, posw, aff, h, reinterpret_cast<unsigned long long*>(w + L.partials), gc_host,
+            nullptr, nullptr);
+        int n_tpart = 0;
+        if (targets != nullptr) {
+            n_tpart = (int)((Nt + 255) / 256);
+            rg_target_bbox_kernel<T><<<n_tpart, 256, 0, stream>>>(targets, Nt, N, posw, reinterpret_cast<unsigned long long*>(w + L.tpartials));
+        }
+        rg_grid_kernel<T><<<1, 1024, 0, stream>>>(h, radius, (long long)src_cap, (long long)cell_cap,
+                                                 PAIR_CAND_BYTES / (int)sizeof(Vec4<T>), force_sx, force_sy,
+                                                 reinterpret_cast<const unsigned long long*>(w + L.partials),
+                                                 (int)((N + WRAP_THREADS - 1) / WRAP_THREADS),
+                                                 reinterpret_cast<const unsigned long long*>(w + L.tpartials), n_tpart);
+        rg_bin_kernel<T, false><<<(unsigned)((nb + 255) / 256), 256, 0, stream>>>(
+            N, Nt, targets, g, posw, h, ccount, cfill, tccount, tcfill, srec, trec, (long long)src_cap, 0);
+    }
     // cell starts of sources and targets in the same three launches; the total of the source counts is the
     // number of source images actually binned (<= the count of rg_wrap when clipping): it becomes header.M
     DYNB_CUDA_OK((exclusive_scan_pair<uint32_t, uint32_t>(ccount, ccount, reinterpret_cast<uint32_t*>(&h->M), tccount, tccount, nullptr,
                                                            &h->ncell_plus1, cell_cap + 1, sums32, stream, cfill, tcfill)));
     rg_bin_kernel<T, true><<<(unsigned)((nb + 255) / 256), 256, 0, stream>>>(
-        N, Nt, targets, g, posw, h, ccount, cfill, tccount, tcfill, srec, trec);
+        N, Nt, targets, g, posw, h, ccount, cfill, tccount, tcfill, srec, trec, (long long)src_cap,
+        host_grid ? PAIR_CAND_BYTES / (int)sizeof(Vec4<T>) : 0);
     const int64_t nf = std::max(src_cap, Nt);
     rg_bin_finalize_kernel<T><<<(unsigned)((nf + 255) / 256), 256, 0, stream>>>(
         N, Nt, targets, g, posw, aff, h, ccount, tccount, srec, trec, spos, sxyz, src_cap, scode, smeta, tpos, tmeta);
