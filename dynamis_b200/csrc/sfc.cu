@@ -476,7 +476,7 @@ struct SelCand { unsigned long long hi, lo; long long w; int g; int pad; };
 static_assert(sizeof(SelCand) == sizeof(SelSplit), "candidates share the unused split-point slots");
 constexpr int SEL_FINISH_SPLITS = 16;        // the fused path's limit on split points
 constexpr int SEL_CAND_CAP = SEL_MAX_SPLITS - SEL_FINISH_SPLITS;   // records behind the split points of state buffer 0
-constexpr int SEL_FINISH_GROUP_MAX = 256;
+constexpr int SEL_FINISH_GROUP_MAX = 128;
 
 __device__ __forceinline__ SelCand sel_load_cand(const SelCand* p)
 {
@@ -507,17 +507,41 @@ __device__ bool sel_finish_warp(const SelSplit& me, int g, const SelCand* cand, 
     }
     __syncwarp();
     if (m == 0 || m > SEL_FINISH_GROUP_MAX) return false;
-    u128 best = ~(u128)0;
-    for (int a = lane; a < m; a += 32) {
-        const SelCand ca = sel_load_cand(cand + member[a]);
-        const u128 Ca = ((u128)ca.hi << 64) | (u128)ca.lo;
-        long long inc = 0;
-        for (int b = 0; b < m; b++) {
-            const SelCand cb = sel_load_cand(cand + member[b]);
-            const u128 Cb = ((u128)cb.hi << 64) | (u128)cb.lo;
-            if (Cb <= Ca) inc += cb.w;
+    // every lane takes the members lane, 32 + lane, ... into registers; each member is then handed round by
+    // shuffles and added to the inclusive weight of every member that is not smaller: no memory in the loop
+    constexpr int KM = SEL_FINISH_GROUP_MAX / 32;
+    const int kmax = (m + 31) >> 5;
+    unsigned long long chi[KM], clo[KM];
+    long long cw[KM], inc[KM];
+#pragma unroll
+    for (int k = 0; k < KM; k++) {
+        chi[k] = clo[k] = ~0ull;
+        cw[k] = 0;
+        inc[k] = 0;
+        const int a = lane + 32 * k;
+        if (a < m) {
+            const SelCand c = sel_load_cand(cand + member[a]);
+            chi[k] = c.hi; clo[k] = c.lo; cw[k] = c.w;
         }
-        if (inc >= me.residual && Ca < best) best = Ca;
+    }
+#pragma unroll
+    for (int kb = 0; kb < KM; kb++) {
+        if (kb < kmax) {
+            const int nb = min(32, m - 32 * kb);
+            for (int lb = 0; lb < nb; lb++) {
+                const unsigned long long bh = __shfl_sync(0xffffffffu, chi[kb], lb), bl = __shfl_sync(0xffffffffu, clo[kb], lb);
+                const long long bw = __shfl_sync(0xffffffffu, cw[kb], lb);
+#pragma unroll
+                for (int ka = 0; ka < KM; ka++)
+                    if (ka < kmax && (bh < chi[ka] || (bh == chi[ka] && bl <= clo[ka]))) inc[ka] += bw;
+            }
+        }
+    }
+    u128 best = ~(u128)0;
+#pragma unroll
+    for (int k = 0; k < KM; k++) {
+        const u128 Ca = ((u128)chi[k] << 64) | (u128)clo[k];
+        if (lane + 32 * k < m && inc[k] >= me.residual && Ca < best) best = Ca;
     }
     unsigned long long bh = (unsigned long long)(best >> 64), bl = (unsigned long long)best;
 #pragma unroll
@@ -539,7 +563,7 @@ __device__ bool sel_finish_warp(const SelSplit& me, int g, const SelCand* cand, 
 // located by reading 256 + 256 counters instead of the whole digit range.
 // With done_counter != nullptr the block that finishes last also advances the split points (one warp
 // each), which saves a launch per level; used while there are few split points.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)   // four blocks per SM for the histogram pass; the rare finish may spill
 sel_hist_kernel(const uint64_t* __restrict__ keys, const int64_t* __restrict__ weights, int64_t n, int idx_bits,
                 int shift, int width, int dbits, const SelSplit* __restrict__ st, SelSplit* __restrict__ st_out, int nsplit,
                 int level, int64_t W, const long long* __restrict__ thresholds, unsigned long long* __restrict__ hist,
