@@ -158,3 +158,27 @@ def check(rc: int, what: str = "") -> None:
         msg = lib().dynb_last_error()
         text = msg.decode() if msg else ""
         raise RuntimeError(f"dynb {what} failed (code {rc}): {text}")
+
+
+class _NoSwitch:
+    """Context manager that does nothing (the device is already the current one)."""
+
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SWITCH = _NoSwitch()
+
+
+def on_device(dev):
+    """``torch.cuda.device(dev)``, or a no-op context when ``dev`` is the current device already: entering and
+    leaving the real guard costs several microseconds of host time in front of every launch sequence."""
+    import torch
+
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
+    if torch.cuda.current_device() == index:
+        return _NO_SWITCH
+    return torch.cuda.device(index)

@@ -94,7 +94,7 @@ class RadiusGraphPlan:
     def fill(self, want_dist_sq: bool = False):
         dev = self.device
         E = self.E
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             edge_index = torch.empty((2, E), dtype=torch.int64, device=dev)
             shifts = torch.empty((E, 3), dtype=torch.float32, device=dev)
             d2 = torch.empty((E,), dtype=self.pos_dtype, device=dev) if want_dist_sq else None
@@ -117,7 +117,7 @@ class RadiusGraphPlan:
         the edge writer itself."""
         dev = self.device
         E = self.E
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             edge_index = torch.empty((2, E), dtype=torch.int64, device=dev)
             unit = torch.empty((E, 3), dtype=torch.float32, device=dev)
             cart = torch.empty((E, 3), dtype=torch.float32, device=dev) if cartesian else None
@@ -154,7 +154,7 @@ def plan_radius_graph(pos, cell, pbc, radius, target_indices=None) -> RadiusGrap
     cell_np = cell.detach().to("cpu").numpy()
     pbc_np = pbc.detach().to("cpu").numpy()
 
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         st = _dev_state(dev)
         # the host-side conversions and the capacities of a geometry are kept by value of (cell, pbc, radius, sizes)
         geo_key = (cell_np.tobytes(), str(cell_np.dtype), pbc_np.tobytes(), float(radius), N, dtype_code)

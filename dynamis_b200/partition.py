@@ -82,7 +82,7 @@ def sfc_partition_labels(pos: torch.Tensor, weights: Optional[torch.Tensor], W: 
             raise RuntimeError(f"weights must have shape [N], got [{weights.size(0)}]")
         weights = weights.to(torch.int64).contiguous()
     L = _lib.lib()
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         labels = torch.empty((N,), dtype=torch.int64, device=dev)
         perm = torch.empty((N,), dtype=torch.int64, device=dev) if return_perm else None
         if N > 0:
@@ -102,7 +102,7 @@ def sfc_keys(pos: torch.Tensor, curve_type: int = 0) -> torch.Tensor:
     keys = torch.empty((N,), dtype=torch.int64, device=dev)
     if N:
         L = _lib.lib()
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             nbytes = ctypes.c_int64()
             _lib.check(L.dynb_sfc_workspace_bytes(N, ctypes.byref(nbytes)), "sfc_workspace_bytes")
             ws = scratch(dev, "sfc", nbytes.value)
@@ -114,7 +114,7 @@ def sfc_keys(pos: torch.Tensor, curve_type: int = 0) -> torch.Tensor:
 def bincount_labels(labels: torch.Tensor, W: int) -> torch.Tensor:
     dev = labels.device
     L = _lib.lib()
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         counts = torch.empty((W,), dtype=torch.int64, device=dev)
         bad = scratch(dev, "bad", 256)
         _lib.check(L.dynb_bincount_i64(labels.data_ptr(), labels.numel(), W, counts.data_ptr(), bad.data_ptr(), _stream(dev)),
@@ -127,7 +127,7 @@ def select_eq(values: torch.Tensor, value: int, gather_src: Optional[torch.Tenso
     dev = values.device
     n = values.numel()
     L = _lib.lib()
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         out = torch.empty((n,), dtype=torch.int64, device=dev)
         cnt = torch.empty((1,), dtype=torch.int64, device=dev)
         nbytes = ctypes.c_int64()
@@ -172,7 +172,7 @@ class AbstractPartitioner:
         pid = info.partition_id.to(device=dev, dtype=torch.int64).contiguous()
         L = _lib.lib()
         words = (W + 31) // 32
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             needed = torch.empty((max(N, 1), words), dtype=torch.int32, device=dev)
             has_foreign = torch.empty((max(N, 1),), dtype=torch.uint8, device=dev)
             if N > 0:
@@ -267,7 +267,7 @@ def kdtree_partition_labels(pos: torch.Tensor, weights: Optional[torch.Tensor], 
             raise RuntimeError(f"weights must have shape [N], got [{weights.size(0)}]")
         weights = weights.to(torch.int64).contiguous()
     L = _lib.lib()
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         labels = torch.empty((N,), dtype=torch.int64, device=dev)
         if N > 0:
             nbytes = ctypes.c_int64()
