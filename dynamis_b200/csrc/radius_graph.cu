@@ -147,11 +147,11 @@ struct GridChoice {
 
 // Cells of edge radius/1.99 scanned +-2 (as the reference, :662,776) unless that would need more than
 // cell_capacity cells; then the cells grow, and once they are wider than the cutoff the scan shrinks to +-1.
-__host__ __device__ inline void rg_choose_shape(GridChoice& gc, double avg, int cand_capacity, int force_sx, int force_sy);
+__host__ __device__ inline void rg_choose_shape(GridChoice& gc, double avg, int cand_capacity, int force_sx, int force_sy, bool allow_wide);
 // avg: expected sources per cell, for the shape of the work items.
 __host__ __device__ inline void rg_choose_grid(const double lo[3], const double ext[3], double radius, long long cell_capacity,
                                                int cand_capacity, double M, double sources_per_volume, int force_sx, int force_sy,
-                                               GridChoice& gc)
+                                               bool allow_wide, GridChoice& gc)
 {
     double res = radius / 1.99;
     long long n[3];
@@ -176,12 +176,15 @@ __host__ __device__ inline void rg_choose_grid(const double lo[3], const double 
     for (int k = 0; k < 3; k++) gc.gmin[k] = lo[k];
     gc.res_inv = 1.0 / res;
     rg_choose_shape(gc, sources_per_volume > 0.0 ? sources_per_volume * res * res * res : M / (double)ncell, cand_capacity, force_sx,
-                    force_sy);
+                    force_sy, allow_wide);
 }
 
 // cells per warp work item (Sx along x, Sy along y): as many target cells as possible while the
 // expected dense candidate list stays within 1.5 shared-memory lists
-__host__ __device__ inline void rg_choose_shape(GridChoice& gc, double avg, int cand_capacity, int force_sx, int force_sy)
+// allow_wide: the mean is taken over a box that the sources fill.  With a target subset the grid can span far more
+// cells than hold sources (a subdomain whose wrapped targets sit on both sides of the periodic box), the mean then
+// says nothing about the lists, and the wide shapes — which sit just under the limit of the hit bits — stay out.
+__host__ __device__ inline void rg_choose_shape(GridChoice& gc, double avg, int cand_capacity, int force_sx, int force_sy, bool allow_wide)
 {
     const int pad = gc.pad;
     // measured on B200 (1 M-atom liquid, 1 M-atom fcc): 2 x 2 cells per warp beat 2 x 1 and 1 x 1 even when the
@@ -196,6 +199,7 @@ __host__ __device__ inline void rg_choose_shape(GridChoice& gc, double avg, int 
     for (int c = 0; c < 5; c++) {
         const int sx = shapes[c][0], sy = shapes[c][1];
         if ((sy + 2 * pad) * (2 * pad + 1) > 32) continue;  // one lane per candidate run
+        if (sx > 2 && !allow_wide) continue;
         const double Lexp = (double)(sx + 2 * pad) * (double)(sy + 2 * pad) * (double)(2 * pad + 1) * (avg > 1e-6 ? avg : 1e-6);
         const bool fits = (sx > 2) ? (1.15 * Lexp + 4.0 * sqrt(Lexp) <= (double)(RG_MASK_SLOTS * 32)) : (Lexp <= budget);
         if (fits || c == 4) { bestx = sx; besty = sy; break; }
@@ -576,7 +580,7 @@ rg_grid_kernel(DevHeader* h, double radius, long long src_capacity, long long ce
         ext[k] = hi - lo[k];
     }
     GridChoice gc;
-    rg_choose_grid(lo, ext, radius, cell_capacity, cand_capacity, (double)h->M, 0.0, force_sx, force_sy, gc);
+    rg_choose_grid(lo, ext, radius, cell_capacity, cand_capacity, (double)h->M, 0.0, force_sx, force_sy, num_tpartials == 0, gc);
     rg_store_grid(*h, gc);
 }
 
@@ -615,7 +619,7 @@ rg_bin_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ targets, Geom<T
         }
         GridChoice gc;
         gc.nx = h.nx; gc.ny = h.ny; gc.nz = h.nz; gc.pad = h.pad;
-        rg_choose_shape(gc, (double)h.M / vol_cells, shape_cand_capacity, 0, 0);
+        rg_choose_shape(gc, (double)h.M / vol_cells, shape_cand_capacity, 0, 0, true);
         hp->group_cells = gc.group_cells;
         hp->group_cells_y = gc.group_cells_y;
         hp->gx = gc.gx;
@@ -1639,7 +1643,7 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
         c = cd;
         const double vol = std::fabs(c[0] * (c[4] * c[8] - c[5] * c[7]) - c[1] * (c[3] * c[8] - c[5] * c[6]) + c[2] * (c[3] * c[7] - c[4] * c[6]));
         const double density = vol > 0.0 ? (double)N / vol : 0.0;  // images repeat the atoms: the same density everywhere in the box
-        rg_choose_grid(lo, ext, radius, (long long)cell_cap, PAIR_CAND_BYTES / (int)sizeof(Vec4<T>), (double)N, density, 0, 0, gc_host);
+        rg_choose_grid(lo, ext, radius, (long long)cell_cap, PAIR_CAND_BYTES / (int)sizeof(Vec4<T>), (double)N, density, 0, 0, true, gc_host);
     }
     {
         DevHeader hi;
