@@ -8,6 +8,8 @@
 // bound that sizes the grid.  In-place operation (out == in) is allowed when the types match.
 #pragma once
 
+#include <cstring>
+
 #include "common.cuh"
 
 namespace dynb {
@@ -40,6 +42,53 @@ __device__ __forceinline__ T block_excl_scan(T v, T* block_total, T* warp_sums /
     return base + x - v;
 }
 
+// A thread's SCAN_ITEMS consecutive elements: two 16-byte loads when the elements are 4 bytes wide, the array is
+// 16-byte aligned and the whole run lies inside the array; element-wise otherwise (and zero past the end).
+template <typename TIn, typename TOut>
+__device__ __forceinline__ void scan_load_items(const TIn* in, int64_t base, int64_t n, TOut (&v)[SCAN_ITEMS])
+{
+    if (sizeof(TIn) == 4 && SCAN_ITEMS == 8 && base + SCAN_ITEMS <= n && (reinterpret_cast<uintptr_t>(in) & 15) == 0) {
+        const uint4 a = *reinterpret_cast<const uint4*>(in + base);
+        const uint4 b = *reinterpret_cast<const uint4*>(in + base + 4);
+        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            TIn t;
+            memcpy(&t, &w[i], 4);
+            v[i] = (TOut)t;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < SCAN_ITEMS; i++) v[i] = (base + i < n) ? (TOut)in[base + i] : (TOut)0;
+    }
+}
+
+// The exclusive prefix of a thread's items, run = prefix in front of the first one: 16-byte stores under the same
+// conditions as the loads above.
+template <typename TOut>
+__device__ __forceinline__ void scan_store_items(TOut* out, int64_t base, int64_t n, TOut run, const TOut (&v)[SCAN_ITEMS])
+{
+    TOut r[SCAN_ITEMS];
+#pragma unroll
+    for (int i = 0; i < SCAN_ITEMS; i++) {
+        r[i] = run;
+        run += v[i];
+    }
+    if (base + SCAN_ITEMS <= n && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (sizeof(TOut) == 4 || sizeof(TOut) == 8)) {
+        constexpr int PER = 16 / (int)sizeof(TOut);
+#pragma unroll
+        for (int q = 0; q < SCAN_ITEMS / PER; q++) {
+            uint4 w;
+            memcpy(&w, &r[q * PER], 16);
+            *reinterpret_cast<uint4*>(out + base + q * PER) = w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < SCAN_ITEMS; i++)
+            if (base + i < n) out[base + i] = r[i];
+    }
+}
+
 __device__ __forceinline__ int64_t scan_count(const uint32_t* n_dev, int64_t n_host)
 {
     if (n_dev == nullptr) return n_host;
@@ -54,10 +103,11 @@ __device__ __forceinline__ void scan_tile_sums_body(const TIn* __restrict__ in, 
     __shared__ TOut warp_sums[SCAN_THREADS / 32];
     const int64_t n = scan_count(n_dev, n_host);
     const int64_t base = (int64_t)blockIdx.x * SCAN_TILE + (int64_t)threadIdx.x * SCAN_ITEMS;
+    TOut v[SCAN_ITEMS];
+    scan_load_items<TIn, TOut>(in, base, n, v);
     TOut s = 0;
 #pragma unroll
-    for (int i = 0; i < SCAN_ITEMS; i++)
-        if (base + i < n) s += (TOut)in[base + i];
+    for (int i = 0; i < SCAN_ITEMS; i++) s += v[i];
     TOut tot;
     (void)block_excl_scan<TOut>(s, &tot, warp_sums);
     if (threadIdx.x == 0) sums[blockIdx.x] = tot;
@@ -119,22 +169,14 @@ __device__ __forceinline__ void scan_apply_body(const TIn* in, const uint32_t* _
     const int64_t n = scan_count(n_dev, n_host);
     const int64_t base = (int64_t)blockIdx.x * SCAN_TILE + (int64_t)threadIdx.x * SCAN_ITEMS;
     TOut v[SCAN_ITEMS];
+    scan_load_items<TIn, TOut>(in, base, n, v);
     TOut s = 0;
 #pragma unroll
-    for (int i = 0; i < SCAN_ITEMS; i++) {
-        v[i] = (base + i < n) ? (TOut)in[base + i] : (TOut)0;
-        s += v[i];
-    }
+    for (int i = 0; i < SCAN_ITEMS; i++) s += v[i];
     TOut tot;
     TOut run = block_excl_scan<TOut>(s, &tot, warp_sums) + sums[blockIdx.x];
-#pragma unroll
-    for (int i = 0; i < SCAN_ITEMS; i++) {
-        if (base + i < n) {
-            out[base + i] = run;
-            if (out_copy != nullptr) out_copy[base + i] = run;
-        }
-        run += v[i];
-    }
+    scan_store_items<TOut>(out, base, n, run, v);
+    if (out_copy != nullptr) scan_store_items<TOut>(out_copy, base, n, run, v);
 }
 
 template <typename TIn, typename TOut>
@@ -190,22 +232,14 @@ __device__ __forceinline__ void scan_apply_fused_body(const TIn* in, const uint3
     const TOut before = scan_prefix_of_sums<TOut>(sums, num_tiles, total_out);
     const int64_t base = (int64_t)blockIdx.x * SCAN_TILE + (int64_t)threadIdx.x * SCAN_ITEMS;
     TOut v[SCAN_ITEMS];
+    scan_load_items<TIn, TOut>(in, base, n, v);
     TOut s = 0;
 #pragma unroll
-    for (int i = 0; i < SCAN_ITEMS; i++) {
-        v[i] = (base + i < n) ? (TOut)in[base + i] : (TOut)0;
-        s += v[i];
-    }
+    for (int i = 0; i < SCAN_ITEMS; i++) s += v[i];
     TOut tot;
     TOut run = block_excl_scan<TOut>(s, &tot, warp_sums) + before;
-#pragma unroll
-    for (int i = 0; i < SCAN_ITEMS; i++) {
-        if (base + i < n) {
-            out[base + i] = run;
-            if (out_copy != nullptr) out_copy[base + i] = run;
-        }
-        run += v[i];
-    }
+    scan_store_items<TOut>(out, base, n, run, v);
+    if (out_copy != nullptr) scan_store_items<TOut>(out_copy, base, n, run, v);
 }
 
 template <typename TIn, typename TOut>
