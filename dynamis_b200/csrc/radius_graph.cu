@@ -1695,7 +1695,7 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
         rg_bin_kernel<T, false><<<(unsigned)((nb + 255) / 256), 256, 0, stream>>>(
             N, Nt, targets, g, posw, h, ccount, cfill, tccount, tcfill, srec, trec, (long long)src_cap, 0);
     }
-    // cell starts of sources and targets in the same three launches; the total of the source counts is the
+    // cell starts of sources and targets in the same two launches (which also set the fill cursors); the total of the source counts is the
     // number of source images actually binned (<= the count of rg_wrap when clipping): it becomes header.M
     DYNB_CUDA_OK((exclusive_scan_pair<uint32_t, uint32_t>(ccount, ccount, reinterpret_cast<uint32_t*>(&h->M), tccount, tccount, nullptr,
                                                            &h->ncell_plus1, cell_cap + 1, sums32, stream, cfill, tcfill)));

@@ -53,9 +53,10 @@ class SFCCurveType(enum.IntEnum):
 
 def launches_per_partition() -> int:
     """Kernels one Morton partition of a million atoms into 8 labels launches (labels only): bounds (1),
-    keys (1), 6 digit levels (histogram; its last block advances the split points), labels (1).  With the
+    keys (1), 6 digit levels (histogram; its last block advances the split points; once the remaining atoms are few
+    the last block settles the split points and the later levels return at once), labels (1).  With the
     curve-order permutation requested the sorted path runs instead: bounds, keys, 8 radix passes x
-    (histogram + 3 scan kernels + scatter), assignment."""
+    (histogram + 2 scan kernels + scatter), assignment."""
     return 1 + 1 + 6 + 1
 
 
