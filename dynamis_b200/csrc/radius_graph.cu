@@ -1619,7 +1619,7 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
     // leaves a hair outside land in the outermost cells (cell_of clamps), which a scan window always includes.
     GridChoice gc_host;
     memset(&gc_host, 0, sizeof(gc_host));
-    const bool host_grid = (targets == nullptr) && g.pbc[0] && g.pbc[1] && g.pbc[2];
+    bool host_grid = (targets == nullptr) && g.pbc[0] && g.pbc[1] && g.pbc[2];
     if (host_grid) {
         double lo[3] = {0, 0, 0}, hi3[3] = {0, 0, 0};
         for (int d = 0; d < 3; d++) {
@@ -1644,6 +1644,9 @@ static int rg_plan(const void* pos_dev, int64_t N, const void* cell_host, const 
         const double vol = std::fabs(c[0] * (c[4] * c[8] - c[5] * c[7]) - c[1] * (c[3] * c[8] - c[5] * c[6]) + c[2] * (c[3] * c[7] - c[4] * c[6]));
         const double density = vol > 0.0 ? (double)N / vol : 0.0;  // images repeat the atoms: the same density everywhere in the box
         rg_choose_grid(lo, ext, radius, (long long)cell_cap, PAIR_CAND_BYTES / (int)sizeof(Vec4<T>), (double)N, density, 0, 0, true, gc_host);
+        // A grid over the whole cell that had to take coarser cells to fit the cell capacity (few atoms in a large
+        // periodic box) is worse than the grid over the data's own bounding box: that case keeps the device path.
+        if (gc_host.res_inv < 0.999 * 1.99 / radius) host_grid = false;
     }
     {
         DevHeader hi;
