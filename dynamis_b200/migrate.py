@@ -117,16 +117,31 @@ def split_positions(N: int, W: int) -> List[int]:
     return out
 
 
-def select_split_atoms(coll: _Coll, sk: torch.Tensor, sg: torch.Tensor, positions: List[int], key_bits: int, id_bits: int):
-    """(key, id) of the atoms at the given global sorted positions of the union of all ranks' (key, id) lists.
-    sk / sg: this rank's keys and ids in (key, id) order.  Every rank gets the same answer."""
+def select_split_atoms(coll, sk: torch.Tensor, sg: torch.Tensor, positions: Optional[List[int]], key_bits: int, id_bits: int,
+                       sw: Optional[torch.Tensor] = None, thresholds: Optional[torch.Tensor] = None):
+    """(key, id) of the W - 1 split atoms of the union of all ranks' (key, id) lists.  sk / sg: this rank's keys
+    and ids in (key, id) order.  Every rank gets the same answer.
+
+    Equal counts: ``positions[s]`` is the global sorted position of split atom s.  Weighted (``sw`` = this rank's
+    non-negative int64 weights in the same order, ``thresholds`` int64 [W - 1], non-decreasing): split atom s is
+    the first atom, in (key, id) order, whose inclusive prefix weight over all ranks reaches ``thresholds[s]``
+    (the reference's rule, dynamis_state/src/csrc/partition/sfc_kernels.cu:165-170, with
+    thresholds[s] = ceil((s + 1) * total / W)).  Both are one digit descent: the number — or the weight — of the
+    atoms at or below a value is a sorted search into this rank's list, summed over the ranks."""
     dev = sk.device
-    S = len(positions)
-    want = torch.tensor(positions, dtype=torch.int64, device=dev) + 1           # count of atoms <= split atom
+    weighted = sw is not None
+    if weighted:
+        want = thresholds.to(device=dev, dtype=torch.int64)
+        cw = torch.cat([torch.zeros(1, dtype=torch.int64, device=dev), torch.cumsum(sw.to(torch.int64), 0)])
+    else:
+        want = torch.tensor(positions, dtype=torch.int64, device=dev) + 1       # count of atoms <= split atom
+        cw = None
+    S = int(want.numel())
     digits = torch.arange(256, dtype=torch.int64, device=dev)
 
-    def descend(sorted_vals, total_bits, base_count, seg_tag=None):
-        """Smallest value v (per split) with #(values <= v) >= want - base_count, by 8-bit digits from the top."""
+    def descend(sorted_vals, total_bits, base_count, cum, seg_tag=None):
+        """Smallest value v (per split) with #(values <= v) >= want - base_count (or their weight, if cum is
+        given: cum[i] = weight of the first i values), by 8-bit digits from the top."""
         prefix = torch.zeros(S, dtype=torch.int64, device=dev)
         levels = (total_bits + 7) // 8
         for l in range(levels):
@@ -136,9 +151,11 @@ def select_split_atoms(coll: _Coll, sk: torch.Tensor, sg: torch.Tensor, position
             dd = digits.clamp(max=(1 << width) - 1)
             cand = prefix[:, None] | (dd[None, :] << shift) | low                           # [S, 256] upper ends of the digit ranges
             q = cand if seg_tag is None else (cand | seg_tag[:, None])
-            cnt = torch.searchsorted(sorted_vals, q.reshape(-1), right=True).reshape(S, 256)
-            if seg_tag is not None:
-                cnt = cnt - seg_start[:, None]
+            idx = torch.searchsorted(sorted_vals, q.reshape(-1), right=True).reshape(S, 256)
+            if cum is None:
+                cnt = idx if seg_tag is None else idx - seg_start[:, None]
+            else:
+                cnt = cum[idx] if seg_tag is None else cum[idx] - cum[seg_start][:, None]
             cnt = coll.all_reduce(cnt.contiguous())
             need = (want - base_count)[:, None]
             d = (cnt < need).sum(dim=1).clamp(max=255)                                     # first digit whose range reaches the rank
@@ -146,20 +163,25 @@ def select_split_atoms(coll: _Coll, sk: torch.Tensor, sg: torch.Tensor, position
         return prefix
 
     zero = torch.zeros(S, dtype=torch.int64, device=dev)
-    K = descend(sk, key_bits, zero)
+    K = descend(sk, key_bits, zero, cw)
     lo = torch.searchsorted(sk, K, right=False)
     hi = torch.searchsorted(sk, K, right=True)
-    below = coll.all_reduce(lo.clone())                                                     # atoms with a smaller key, all ranks
+    below = coll.all_reduce((cw[lo] if weighted else lo).clone())                           # atoms (weight) with a smaller key, all ranks
     # ids of the atoms that share the split key, per split point, tagged so that one sorted array serves all
     tag_shift = 40
     if id_bits > tag_shift:
         raise RuntimeError("global atom ids beyond 2^40 are not supported")
     lens = (hi - lo).tolist()
-    seg = [sg[a:b] | (s << tag_shift) for s, (a, b) in enumerate(zip(lo.tolist(), hi.tolist()))]
+    bounds = list(zip(lo.tolist(), hi.tolist()))
+    seg = [sg[a:b] | (s << tag_shift) for s, (a, b) in enumerate(bounds)]
     ties = torch.cat(seg) if seg else sg[:0]
     seg_start = torch.tensor([sum(lens[:s]) for s in range(S)], dtype=torch.int64, device=dev)
     seg_tag = torch.arange(S, dtype=torch.int64, device=dev) << tag_shift
-    G = descend(ties, id_bits, below, seg_tag)
+    cum_t = None
+    if weighted:
+        tw = torch.cat([sw[a:b] for a, b in bounds]) if bounds else sw[:0]
+        cum_t = torch.cat([torch.zeros(1, dtype=torch.int64, device=dev), torch.cumsum(tw.to(torch.int64), 0)])
+    G = descend(ties, id_bits, below, cum_t, seg_tag)
     return K, G
 
 
@@ -207,12 +229,20 @@ class DistributedSimState:
         return st
 
     # ------------------------------------------------------------------ steps 1-4
-    def new_labels(self) -> torch.Tensor:
+    def new_labels(self, weights: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Label in [0, W) of every atom this rank holds, equal to what the partition of the gathered system
-        gives (Morton or "Hilbert" keys, equal counts, ties by global id)."""
+        gives (Morton or "Hilbert" keys, ties by global id): equal counts, or — with ``weights``, one
+        non-negative integer per atom this rank holds, e.g. its degree — equal weight (the reference's
+        weighted cut, dynamis_state/src/csrc/partition/sfc_kernels.cu:139-173)."""
         if self.N < self.W:
             raise RuntimeError("fewer atoms than ranks")
         L, dev, n = _lib.lib(), self.device, self.pos.shape[0]
+        if weights is not None:
+            if weights.shape != (n,):
+                raise RuntimeError(f"weights must have shape [{n}], got {list(weights.shape)}")
+            weights = weights.to(device=dev, dtype=torch.int64)
+            if n and int(weights.min()) < 0:
+                raise RuntimeError("weights must be non-negative")
         with torch.cuda.device(dev):
             mm = torch.zeros(32, dtype=torch.float32, device=dev)
             _lib.check(L.dynb_sfc_minmax(self.pos.data_ptr(), n, mm.data_ptr(), _stream(dev)), "sfc_minmax")
@@ -230,7 +260,14 @@ class DistributedSimState:
             sk, perm = _radix_sort_pairs(keys, key_bits)       # stable: equal keys stay in ascending global id
             sg = self.gid[perm] if n else self.gid
             id_bits = max(1, (self.N - 1).bit_length())
-            K, G = select_split_atoms(self.coll, sk, sg, split_positions(self.N, self.W), key_bits, id_bits)
+            if weights is None:
+                K, G = select_split_atoms(self.coll, sk, sg, split_positions(self.N, self.W), key_bits, id_bits)
+            else:
+                total = int(self.coll.all_reduce(weights.sum().reshape(1).clone())[0])
+                if total == 0:      # the reference labels everything 0 then (sfc_kernels.cu:160-163)
+                    return torch.zeros(n, dtype=torch.int64, device=dev)
+                thr = torch.tensor([max(1, ((s + 1) * total + self.W - 1) // self.W) for s in range(self.W - 1)], dtype=torch.int64)
+                K, G = select_split_atoms(self.coll, sk, sg, None, key_bits, id_bits, sw=weights[perm] if n else weights, thresholds=thr)
             labels = torch.empty(n, dtype=torch.int64, device=dev)
             _lib.check(L.dynb_label_by_splits(keys.data_ptr(), self.gid.data_ptr(), n, K.data_ptr(), G.data_ptr(), self.W - 1,
                                               labels.data_ptr(), _stream(dev)), "label_by_splits")
@@ -318,9 +355,10 @@ class DistributedSimState:
         self.info = info
         return info
 
-    def repartition(self) -> PartitionMessagePassingInfo:
-        """The reference's sync_and_repartition (simulatorState.py:136-199) on distributed state."""
-        labels = self.new_labels()
+    def repartition(self, weights: Optional[torch.Tensor] = None) -> PartitionMessagePassingInfo:
+        """The reference's sync_and_repartition (simulatorState.py:136-199) on distributed state; ``weights``
+        (per atom this rank holds) selects the weighted cut."""
+        labels = self.new_labels(weights)
         self.owned_labels = labels
         self._migrate(labels)
         return self.rebuild_halo()

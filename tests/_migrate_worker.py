@@ -87,6 +87,13 @@ def main():
         tot = torch.tensor([st.last["atoms_leaving"]], dtype=torch.int64, device="cpu" if shared else dev)
         dist.all_reduce(tot)
         assert int(tot) == moved, (int(tot), moved)
+        # weighted cut (the reference's mode for degree-balanced partitions): every rank passes the degrees of the
+        # atoms it holds; owners and halo maps must equal those of the gathered system's weighted partition
+        if name != "triclinic/morton":
+            deg = O.radius_graph(pos, cell, [1, 1, 1], np.float32(rc))["counts"].astype(np.int64)
+            st.repartition(weights=torch.as_tensor(deg[st.gid.cpu().numpy()], device=dev))
+            pid3 = O.sfc_partition(pos, deg, W, curve)
+            check(st, rank, W, pos, vel, cell, [1, 1, 1], rc + buf, curve, pid3, f"{name}: weighted repartition")
         # the halo plan drives a real exchange of the owned rows: ghost rows equal the owners' rows
         if not shared:
             ex = D.GPUDirectExchanger(wait_ns=10_000_000_000)
