@@ -596,7 +596,9 @@ rg_bin_kernel(int64_t N, int64_t Nt, const int64_t* __restrict__ targets, Geom<T
               uint4* __restrict__ srec, uint2* __restrict__ trec, long long src_capacity, int shape_cand_capacity)
 {
     const DevHeader h = *hp;
-    if (h.status & RG_FATAL) return;
+    // the counting pass still runs when only the image capacity is short (it writes nothing but the cell counters): the
+    // prefix sum's total then leaves the true number of images in header.M for the caller's second attempt
+    if (h.status & (SCATTER ? RG_FATAL : (RG_FATAL & ~(uint32_t)DYNB_RG_SRC_OVERFLOW))) return;
     if (SCATTER && h.M > (unsigned long long)src_capacity) {
         // more images than the caller's buffers hold (header.M is the prefix sum's total by now; with a grid chosen on
         // the host this is the first place that knows): nothing is placed, the plan is repeated with a larger capacity

@@ -186,7 +186,7 @@ def plan_radius_graph(pos, cell, pbc, radius, target_indices=None) -> RadiusGrap
             stream.synchronize()
             status = int(hdr.status)
             if status & _lib.RG_SRC_OVERFLOW and attempt < 2:
-                src_cap = int(hdr.M) + 1024
+                src_cap = max(int(hdr.M) + 1024, 2 * src_cap)
                 st["geo"][geo_key] = (cell_h, pbc_h, radius, src_cap, cell_cap)  # the next call starts with the larger capacity
                 continue
             break

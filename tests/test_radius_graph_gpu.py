@@ -311,6 +311,30 @@ def test_edge_distances_fp32(cuda):
     np.testing.assert_allclose(d2.cpu().numpy()[order_t], g["d2"][order_o], rtol=1e-6)
 
 
+@pytest.mark.parametrize("periodic", [True, False])
+def test_image_capacity_overflow_is_reported_and_the_plan_repeated(cuda, periodic):
+    """A capacity for the periodic images that turns out too small must come back as a status bit with the true
+    count (so that the caller can repeat the plan), not as a write past the buffers: on the fully periodic path the
+    scatter pass is the first to know, otherwise the grid kernel.  The host layer's capacity cache is made too
+    small on purpose; the call must still return the right graph."""
+    from dynamis_b200 import graph as G
+
+    pos, cell, pbc = _cubic(4000, 30.0, 5)
+    if not periodic:
+        pbc = [True, True, False]
+    geo = G._dev_state(cuda)["geo"]
+    geo.clear()
+    try:
+        _check_vs_oracle(pos, cell, pbc, 5.0, cuda, what="first call")
+        assert len(geo) == 1, "the first call should have left its capacities in the cache"
+        (key, (cell_h, pbc_h, radius, src_cap, cell_cap)), = geo.items()
+        geo[key] = (cell_h, pbc_h, radius, 1000, cell_cap)      # fewer slots than atoms, let alone images
+        _check_vs_oracle(pos, cell, pbc, 5.0, cuda, what="after the overflow")
+        assert geo[key][3] > 4000, "the repeated plan should have left the larger capacity in the cache"
+    finally:
+        geo.clear()
+
+
 # ------------------------------------------------------------------ against the reference's own kernels
 
 def _run_ref(ref_ops, pos, cell, pbc, r, dev, targets=None):
