@@ -497,7 +497,7 @@ def run(args, rank: int, world: int, dev: torch.device):
                     "note": "positions in from pinned host memory, degrees and edge count out; the edge list stays on the device, "
                             "as with the API it replaces (CUDA tensors for a CUDA consumer)"},
             "clocks": clocks,
-            "gpu_launches": D.launches_per_graph() + 6 * 2,
+            "gpu_launches": D.launches_per_graph(target_subset=True) + 6 * 2,
         }
         print(json.dumps(line), flush=True)
     dist.barrier()

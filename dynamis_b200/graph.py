@@ -331,13 +331,18 @@ def owned_graph(positions: torch.Tensor, cell: torch.Tensor, pbc: torch.Tensor, 
     return plan.fill_glue(cell, negate_shifts, cartesian)
 
 
-def launches_per_graph() -> int:
+def launches_per_graph(target_subset: bool = False, fully_periodic: bool = True) -> int:
     """Kernels one radius_graph_pbc call launches on a fully periodic cell: init (header, counters, degrees), wrap
     (which also counts the images into their cells: the grid follows from the cell), 2 scan kernels (source and
     target cell starts together), scatter, finalize, count pass (degrees included), 2 scan kernels (edge offsets),
     two edge-writing launches (the one driven by the hit bits of the count pass and the one that recomputes
     distances; the device decides which of them does the work, the other returns at once; with distances
     requested only the second is launched).  Two more (grid from the data's bounding box, cell histogram) when a
-    direction is not periodic, and two more again (the targets' bounding box, the list of groups with targets) with
-    a target subset."""
-    return 11
+    direction is not periodic or a target subset is given, and two more again (the targets' bounding box, the
+    list of groups with targets) with a target subset."""
+    n = 11
+    if target_subset or not fully_periodic:
+        n += 2
+    if target_subset:
+        n += 2
+    return n
