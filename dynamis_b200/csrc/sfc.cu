@@ -565,11 +565,11 @@ __device__ bool sel_finish_warp(const SelSplit& me, int g, const SelCand* cand, 
 // each), which saves a launch per level; used while there are few split points.
 __global__ void __launch_bounds__(256, 4)   // four blocks per SM for the histogram pass; the rare finish may spill
 sel_hist_kernel(const uint64_t* __restrict__ keys, const int64_t* __restrict__ weights, int64_t n, int idx_bits,
-                int shift, int width, int dbits, const SelSplit* __restrict__ st, SelSplit* __restrict__ st_out, int nsplit,
+                int shift, int width, int dbits, const SelSplit* st, SelSplit* __restrict__ st_out, int nsplit,
                 int level, int64_t W, const long long* __restrict__ thresholds, unsigned long long* __restrict__ hist,
                 unsigned long long* __restrict__ hist_next, int64_t table_words, unsigned int* __restrict__ done_counter,
                 int fine_private, SelCand* __restrict__ cand, unsigned int* __restrict__ cand_count,
-                unsigned int* __restrict__ finished, SelSplit* __restrict__ st_other)
+                unsigned int* __restrict__ finished, SelSplit* st_other /* the buffer st points into: no restrict */)
 {
     // fine_private (first level, unit weights, width <= 14 only): the digit counters of this block are kept in
     // shared memory and added to the table once at the end -- for keys that crowd into a few digits (the
